@@ -38,7 +38,12 @@ GROUPS = {"ragged": ["lib", "linear_generic", "dense_gemm", "norm_act", "gated_d
                      "attention_api", "elementwise"],
           # latent attention + routed experts: both linear kernels (the tcgen05 one also in its grouped form), norms, the latent mixers incl. the
           # split-KV latent decode kernel, the expert kernels, argmax
-          "latent": ["lib", "linear_generic", "dense_gemm", "norm_act", "latent_attention", "moe_ragged", "mla", "elementwise"]}
+          "latent": ["lib", "linear_generic", "dense_gemm", "norm_act", "latent_attention", "moe_ragged", "mla", "elementwise"],
+          # state-space / linear-attention mixers beside softmax attention, with dense or routed feed-forwards: both linear kernels (the tcgen05 one also
+          # grouped), norms, the recurrences, the SIMT attention over the paged cache and the tensor-core prefill kernel it hands 128-wide heads to, the
+          # head gate of the latent mixers, the expert kernels
+          "hybrid": ["lib", "linear_generic", "dense_gemm", "norm_act", "linear_recurrence", "attention_varlen", "attention_prefill", "latent_attention",
+                     "moe_ragged", "elementwise"]}
 
 
 def so_path(group=None) -> str:

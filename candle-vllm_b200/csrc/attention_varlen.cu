@@ -8,7 +8,9 @@
 //                           q row and the whole k row (weights of that length; optional), rotation of the first rot_dims entries
 //                           of every head, entry i paired with i + rot_dims/2, by a cos/sin table [max_pos, rot_dims/2] that
 //                           already carries any frequency scaling and magnitude factor (optional), q written out in f32, k and v
-//                           written into the paged cache at slot_mapping[t] (K [nb, bs, G, dk], V [nb, bs, G, dv]).
+//                           written into the paged cache at slot_mapping[t] (K [nb, bs, G, dk], V [nb, bs, G, dv]).  The _ex form
+//                           adds a query temperature (q times 1 + coef ln(floor((p + 1) / every) + 1) at position p) and values
+//                           stored at unit root mean square per head.
 //   paged_attention_varlen  one warp per (token, head); keys in tiles of 32 (a lane scores one key, the tile's values are then
 //                           accumulated with lanes across the value columns), online softmax in f32.
 #include <stdlib.h>
@@ -24,7 +26,8 @@ __global__ void __launch_bounds__(256)
 qk_norm_rope_cache_kernel(const float* __restrict__ qkv, int64_t ld, const float* __restrict__ q_norm_w, const float* __restrict__ k_norm_w,
                           const float* __restrict__ cos_t, const float* __restrict__ sin_t, const int32_t* __restrict__ positions,
                           const int64_t* __restrict__ slot_mapping, TQ* __restrict__ q_out, TC* __restrict__ k_cache,
-                          TC* __restrict__ v_cache, int H, int G, int dk, int dv, int rot_dims, float eps) {
+                          TC* __restrict__ v_cache, int H, int G, int dk, int dv, int rot_dims, float eps, float q_temp_coef, int q_temp_every,
+                          int v_unit_rms) {
     pdl_wait();
     pdl_trigger();
     __shared__ float red[2][8];
@@ -42,9 +45,11 @@ qk_norm_rope_cache_kernel(const float* __restrict__ qkv, int64_t ld, const float
 #pragma unroll
         for (int i = 0; i < 8; ++i) { sq += red[0][i]; sk += red[1][i]; }
     }
-    const float qsc = q_norm_w ? 1.0f / sqrtf(sq / (float)nq + eps) : 1.0f;
-    const float ksc = k_norm_w ? 1.0f / sqrtf(sk / (float)nk + eps) : 1.0f;
     const int pos = positions[t];
+    // query temperature: the whole query grows with the logarithm of the number of full runs of `every` places before it
+    const float q_temp = q_temp_every > 0 ? 1.0f + q_temp_coef * logf((float)((pos + 1) / q_temp_every) + 1.0f) : 1.0f;
+    const float qsc = (q_norm_w ? 1.0f / sqrtf(sq / (float)nq + eps) : 1.0f) * q_temp;
+    const float ksc = k_norm_w ? 1.0f / sqrtf(sk / (float)nk + eps) : 1.0f;
     const int half = rot_dims >> 1;
     const int64_t slot = slot_mapping[t];
     for (int e = threadIdx.x; e < nq + nk; e += 256) {
@@ -65,8 +70,20 @@ qk_norm_rope_cache_kernel(const float* __restrict__ qkv, int64_t ld, const float
         if (is_q) q_out[(int64_t)t * nq + idx] = from_f32<TQ>(val);
         else if (slot >= 0) k_cache[slot * nk + idx] = from_f32<TC>(val);
     }
-    if (slot >= 0)
-        for (int i = threadIdx.x; i < nv; i += 256) v_cache[slot * nv + i] = from_f32<TC>(row[nq + nk + i]);
+    if (slot < 0) return;
+    if (v_unit_rms) {
+        // every value head is stored at unit root mean square: a warp takes whole heads
+        const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+        for (int g = warp; g < G; g += 8) {
+            const float* vr = row + nq + nk + g * dv;
+            float ss = 0.f;
+            for (int i = lane; i < dv; i += 32) { const float v = vr[i]; ss = fmaf(v, v, ss); }
+            const float sc = 1.0f / sqrtf(warp_sum(ss) / (float)dv + eps);
+            for (int i = lane; i < dv; i += 32) v_cache[slot * nv + g * dv + i] = from_f32<TC>(vr[i] * sc);
+        }
+        return;
+    }
+    for (int i = threadIdx.x; i < nv; i += 256) v_cache[slot * nv + i] = from_f32<TC>(row[nq + nk + i]);
 }
 
 // Steps made of single tokens: a query at position i sees the keys chunk_start .. i with chunk_start = floor(i / chunk) * chunk.  When
@@ -165,6 +182,14 @@ void qk_norm_rope_cache(const float* qkv, int64_t ld, const float* q_norm_w, con
                         int32_t max_pos, const int32_t* positions, const int64_t* slot_mapping, void* q_out, void* key_cache, void* value_cache,
                         int32_t num_tokens, int32_t num_heads, int32_t num_kv_heads, int32_t dk, int32_t dv, int32_t rot_dims, float eps,
                         int32_t cache_dtype, int32_t q_dtype, int64_t stream) {
+    qk_norm_rope_cache_ex(qkv, ld, q_norm_w, k_norm_w, cos_t, sin_t, max_pos, positions, slot_mapping, q_out, key_cache, value_cache, num_tokens, num_heads,
+                          num_kv_heads, dk, dv, rot_dims, eps, 0.f, 0, 0, cache_dtype, q_dtype, stream);
+}
+
+void qk_norm_rope_cache_ex(const float* qkv, int64_t ld, const float* q_norm_w, const float* k_norm_w, const float* cos_t, const float* sin_t,
+                           int32_t max_pos, const int32_t* positions, const int64_t* slot_mapping, void* q_out, void* key_cache, void* value_cache,
+                           int32_t num_tokens, int32_t num_heads, int32_t num_kv_heads, int32_t dk, int32_t dv, int32_t rot_dims, float eps,
+                           float q_temp_coef, int32_t q_temp_every, int32_t v_unit_rms, int32_t cache_dtype, int32_t q_dtype, int64_t stream) {
     if (num_tokens == 0) return;
     B200_REQUIRE(qkv && positions && slot_mapping && q_out && key_cache && value_cache, kErrBadArg, "qk_norm_rope_cache: null pointer");
     B200_REQUIRE((q_norm_w == nullptr) == (k_norm_w == nullptr) && (cos_t == nullptr) == (sin_t == nullptr), kErrBadArg,
@@ -174,7 +199,7 @@ void qk_norm_rope_cache(const float* qkv, int64_t ld, const float* q_norm_w, con
                  kErrBadArg, "qk_norm_rope_cache: bad sizes");
     cudaStream_t st = as_stream(stream);
 #define QNRC(TC, TQ) launch_pdl(qk_norm_rope_cache_kernel<TC, TQ>, dim3(num_tokens), dim3(256), 0, st, qkv, ld, q_norm_w, k_norm_w, cos_t, sin_t, positions, \
-        slot_mapping, (TQ*)q_out, (TC*)key_cache, (TC*)value_cache, num_heads, num_kv_heads, dk, dv, rot_dims, eps)
+        slot_mapping, (TQ*)q_out, (TC*)key_cache, (TC*)value_cache, num_heads, num_kv_heads, dk, dv, rot_dims, eps, q_temp_coef, q_temp_every, v_unit_rms)
     if (cache_dtype == B200_F32 && q_dtype == B200_F32) QNRC(float, float);
     else if (cache_dtype == B200_BF16 && q_dtype == B200_F32) QNRC(__nv_bfloat16, float);
     else if (cache_dtype == B200_BF16 && q_dtype == B200_BF16) QNRC(__nv_bfloat16, __nv_bfloat16);

@@ -1,0 +1,470 @@
+// linear_recurrence.cu -- sequence mixers whose memory is a fixed-size f32 state per sequence, for ragged steps (portions of prompts
+// beside single decoded tokens in one launch).  Entry b's rows continue the sequence whose state sits in slot seq_slots[b];
+// seq_start[b] == 0 means "new sequence": what the slot holds is ignored (taken as zero), so a slot is never cleared.
+//
+//   causal_conv_ex        y[t, c] = act(sum_j taps[c, j] * in[t - K + 1 + j, c] + out_bias[c]) (+ in[t, c]), in = x + in_bias, zeros before
+//                         the sequence's start; the K - 1 inputs before a portion come from conv_state [slots, K-1, C], which is then
+//                         rolled forward over the portion.  act = none or SiLU; the "+ in" form is a convolution added to its own input.
+//   block_diag_linear     out[t, b M + j] = sum_i w[b, j, i] x[t, b N + i] + bias[b M + j]: one matrix per block of N neighbouring
+//                         channels, true 32-bit products (the gates of a recurrence).
+//   gated_linear_scan     per channel  S_t = a_t S_(t-1) + sqrt(1 - a_t^2) i_t u_t,  a_t = exp(-c r_t softplus(lam)),  r, i = sigmoid of
+//                         the block-diagonal products;  out_t = S_t * gelu_tanh(y_t + y_bias).
+//   linear_attention      per head, S [dk, dv]:  S_t = a_t S_(t-1) + b_t k_t v_t^T,  o_t = S_t^T q_t, in two gatings:
+//                           fixed decay      a = decay[h], b = 1;
+//                           exponential      a_t = e^(f_t + m_(t-1) - m_t), b_t = e^(i_t - m_t) with the running maximum m_t = max(f_t + m_(t-1), i_t),
+//                                            m_0 = 0, i = cap tanh(. / cap), f = logsigmoid(cap tanh(. / cap)); a normaliser n_t = a_t n_(t-1) + b_t k_t
+//                                            rides along and o_t = S_t^T q_t / (max(|n_t . q_t|, e^(-m_t)) + 1e-6).  n and m are stored once per
+//                                            block of 16 value columns, so that no block reads what another one writes.
+//                         A block of four warps owns 16 value columns of one head of one entry; inside a warp the key rows are split eight
+//                         ways (lane = 4 * part + column) with the lane's rows of S (and of n) in registers; tokens come in tiles of 16
+//                         staged through shared memory with the activation already applied, the per-token coefficients worked out once
+//                         per tile (the chain of maxima by one lane, the exponentials by sixteen).  Every sum has a fixed order, so
+//                         portions of any size leave the same state bit for bit.  State S is stored [slot, head, column, row].
+#include "common.cuh"
+
+namespace b200 {
+namespace {
+
+__device__ __forceinline__ float silu_f(float z) { return z / (1.0f + expf(-z)); }
+__device__ __forceinline__ float sigmoid_f(float z) { return 1.0f / (1.0f + expf(-z)); }
+__device__ __forceinline__ float softplus_f(float z) { return z > 20.f ? z : log1pf(expf(z)); }
+__device__ __forceinline__ float log_sigmoid_f(float z) { return fminf(z, 0.f) - log1pf(expf(-fabsf(z))); }
+__device__ __forceinline__ float gelu_tanh_f(float z) {
+    const float c = 0.7978845608028654f;       // sqrt(2 / pi)
+    return 0.5f * z * (1.0f + tanhf(c * (z + 0.044715f * z * z * z)));
+}
+
+template <typename TOut>
+__global__ void __launch_bounds__(128)
+causal_conv_ex_kernel(const float* __restrict__ x, int64_t ldx, const float* __restrict__ in_bias, const float* __restrict__ taps,
+                      const float* __restrict__ out_bias, const float* __restrict__ conv_state, TOut* __restrict__ y, int64_t ldy,
+                      const int32_t* __restrict__ token_seq, const int32_t* __restrict__ cu_seqlens, const int32_t* __restrict__ seq_slots,
+                      const int32_t* __restrict__ seq_start, int C, int K, int act, int add_input) {
+    pdl_wait();
+    pdl_trigger();
+    const int c = blockIdx.x * 128 + threadIdx.x;
+    const int t = blockIdx.y;
+    if (c >= C) return;
+    const int b = token_seq[t];
+    const int i = t - cu_seqlens[b];
+    const bool fresh = seq_start[b] == 0;
+    const float* st = conv_state + (int64_t)seq_slots[b] * (K > 1 ? K - 1 : 1) * C;
+    const float ib = in_bias ? in_bias[c] : 0.f;
+    float acc = 0.f, cur = 0.f;
+    for (int d = K - 1; d >= 0; --d) {            // oldest input first
+        const int src = i - d;
+        float v;
+        if (src >= 0) v = x[(int64_t)(t - d) * ldx + c] + ib;
+        else v = fresh ? 0.f : st[(int64_t)(K - 1 + src) * C + c];
+        if (d == 0) cur = v;
+        acc = fmaf(taps[(int64_t)c * K + (K - 1 - d)], v, acc);
+    }
+    if (out_bias) acc += out_bias[c];
+    if (act == 1) acc = silu_f(acc);
+    if (add_input) acc += cur;
+    y[(int64_t)t * ldy + c] = from_f32<TOut>(acc);
+}
+
+__global__ void __launch_bounds__(128)
+causal_conv_roll_kernel(const float* __restrict__ x, int64_t ldx, const float* __restrict__ in_bias, float* __restrict__ conv_state,
+                        const int32_t* __restrict__ cu_seqlens, const int32_t* __restrict__ seq_slots, const int32_t* __restrict__ seq_start, int C, int K) {
+    pdl_wait();
+    pdl_trigger();
+    const int c = blockIdx.x * 128 + threadIdx.x;
+    const int b = blockIdx.y;
+    if (c >= C) return;
+    const int t0 = cu_seqlens[b], n = cu_seqlens[b + 1] - t0;
+    if (n <= 0) return;
+    const bool fresh = seq_start[b] == 0;
+    const float ib = in_bias ? in_bias[c] : 0.f;
+    float* st = conv_state + (int64_t)seq_slots[b] * (K - 1) * C;
+    // the sequence's inputs so far are [old state rows 0 .. K-2][portion rows 0 .. n-1]; the last K-1 of them stay.  Row j of the new
+    // state is element n + j of that list: j ascends and n >= 1, so an old row is read before it is overwritten.
+    for (int j = 0; j < K - 1; ++j) {
+        const int e = n + j;
+        float v;
+        if (e >= K - 1) v = x[(int64_t)(t0 + e - (K - 1)) * ldx + c] + ib;
+        else v = fresh ? 0.f : st[(int64_t)e * C + c];
+        st[(int64_t)j * C + c] = v;
+    }
+}
+
+// ---- block-diagonal f32 product ---------------------------------------------------------------------------------------------------
+constexpr int kBM = 64, kBN = 64, kBK = 16;
+
+__global__ void __launch_bounds__(256)
+block_diag_linear_kernel(const float* __restrict__ x, int64_t ldx, const float* __restrict__ w, const float* __restrict__ bias, float* __restrict__ y,
+                         int64_t ldy, int T, int M, int N) {
+    pdl_wait();
+    pdl_trigger();
+    __shared__ float xs[kBK][kBM + 4], ws[kBK][kBN + 4];
+    const int blk = blockIdx.z;
+    const float* xb = x + (int64_t)blk * N;
+    const float* wb = w + (int64_t)blk * M * N;
+    const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;
+    const int row0 = blockIdx.y * kBM, col0 = blockIdx.x * kBN;
+    float acc[4][4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) acc[i][j] = 0.f;
+    for (int k0 = 0; k0 < N; k0 += kBK) {
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const int idx = threadIdx.x + i * 256, r = idx >> 4, c = idx & 15;
+            const int gr = row0 + r, gc = k0 + c, wr = col0 + r;
+            xs[c][r] = (gr < T && gc < N) ? xb[(int64_t)gr * ldx + gc] : 0.f;
+            ws[c][r] = (wr < M && gc < N) ? wb[(int64_t)wr * N + gc] : 0.f;
+        }
+        __syncthreads();
+#pragma unroll
+        for (int kk = 0; kk < kBK; ++kk) {
+            float a[4], b[4];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) { a[i] = xs[kk][ty * 4 + i]; b[i] = ws[kk][tx * 4 + i]; }
+#pragma unroll
+            for (int i = 0; i < 4; ++i)
+#pragma unroll
+                for (int j = 0; j < 4; ++j) acc[i][j] = fmaf(a[i], b[j], acc[i][j]);
+        }
+        __syncthreads();
+    }
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const int gr = row0 + ty * 4 + i;
+        if (gr >= T) continue;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const int gc = col0 + tx * 4 + j;
+            if (gc < M) y[(int64_t)gr * ldy + (int64_t)blk * M + gc] = acc[i][j] + (bias ? bias[(int64_t)blk * M + gc] : 0.f);
+        }
+    }
+}
+
+// few rows: a warp owns one output column of one block and up to 4 rows, lanes stride the block's inputs
+__global__ void __launch_bounds__(256)
+block_diag_rows_kernel(const float* __restrict__ x, int64_t ldx, const float* __restrict__ w, const float* __restrict__ bias, float* __restrict__ y,
+                       int64_t ldy, int T, int M, int N) {
+    pdl_wait();
+    pdl_trigger();
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int blk = blockIdx.z;
+    const int col = blockIdx.x * 8 + warp;
+    const int r0 = blockIdx.y * 4;
+    if (col >= M) return;
+    const float* wr = w + ((int64_t)blk * M + col) * N;
+    const float* xb = x + (int64_t)blk * N;
+    float acc[4] = {0.f, 0.f, 0.f, 0.f};
+    for (int i = lane; i < N; i += 32) {
+        const float wv = wr[i];
+#pragma unroll
+        for (int r = 0; r < 4; ++r)
+            if (r0 + r < T) acc[r] = fmaf(xb[(int64_t)(r0 + r) * ldx + i], wv, acc[r]);
+    }
+#pragma unroll
+    for (int r = 0; r < 4; ++r) {
+        const float s = warp_sum(acc[r]);
+        if (lane == 0 && r0 + r < T) y[(int64_t)(r0 + r) * ldy + (int64_t)blk * M + col] = s + (bias ? bias[(int64_t)blk * M + col] : 0.f);
+    }
+}
+
+// ---- the gated scan ------------------------------------------------------------------------------------------------------------------
+// One thread per (entry, channel); the next rows' operands are fetched while the current row is applied.  gates f32 [T, blocks, 2 n]: per
+// block the recurrence gate's pre-activations, then the input gate's.
+template <typename TOut>
+__global__ void __launch_bounds__(64)
+gated_linear_scan_kernel(const float* __restrict__ u, int64_t ldu, const float* __restrict__ gates, int64_t ldg, const float* __restrict__ lam,
+                         const float* __restrict__ ypre, int64_t ldy, const float* __restrict__ y_bias, float* __restrict__ state, TOut* __restrict__ out,
+                         const int32_t* __restrict__ cu_seqlens, const int32_t* __restrict__ seq_slots, const int32_t* __restrict__ seq_start, int C, int n,
+                         float decay_scale) {
+    pdl_wait();
+    pdl_trigger();
+    const int c = blockIdx.x * 64 + threadIdx.x;
+    const int b = blockIdx.y;
+    if (c >= C) return;
+    const int t0 = cu_seqlens[b], t1 = cu_seqlens[b + 1];
+    if (t1 <= t0) return;
+    float* sp = state + (int64_t)seq_slots[b] * C + c;
+    float S = seq_start[b] == 0 ? 0.f : *sp;
+    const float k = -decay_scale * softplus_f(lam[c]);
+    const float yb = y_bias ? y_bias[c] : 0.f;
+    const int blk = c / n, j = c - blk * n;
+    const int rc = blk * 2 * n + j, ic = rc + n;
+    constexpr int kAhead = 4;
+    float gr[kAhead], gi[kAhead], uu[kAhead], yy[kAhead];
+#pragma unroll
+    for (int a = 0; a < kAhead; ++a) {
+        const int t = min(t0 + a, t1 - 1);
+        gr[a] = gates[(int64_t)t * ldg + rc]; gi[a] = gates[(int64_t)t * ldg + ic]; uu[a] = u[(int64_t)t * ldu + c]; yy[a] = ypre[(int64_t)t * ldy + c];
+    }
+    for (int tb = t0; tb < t1; tb += kAhead) {
+        float cr[kAhead], ci[kAhead], cu[kAhead], cy[kAhead];
+#pragma unroll
+        for (int a = 0; a < kAhead; ++a) { cr[a] = gr[a]; ci[a] = gi[a]; cu[a] = uu[a]; cy[a] = yy[a]; }
+#pragma unroll
+        for (int a = 0; a < kAhead; ++a) {
+            const int t = min(tb + kAhead + a, t1 - 1);
+            gr[a] = gates[(int64_t)t * ldg + rc]; gi[a] = gates[(int64_t)t * ldg + ic]; uu[a] = u[(int64_t)t * ldu + c]; yy[a] = ypre[(int64_t)t * ldy + c];
+        }
+#pragma unroll
+        for (int a = 0; a < kAhead; ++a) {
+            if (tb + a >= t1) break;
+            const float la = k * sigmoid_f(cr[a]);                     // log a_t <= 0
+            const float at = expf(la);
+            const float mult = sqrtf(-expm1f(2.0f * la));               // sqrt(1 - a^2) without cancellation near a = 1
+            S = fmaf(at, S, mult * sigmoid_f(ci[a]) * cu[a]);
+            out[(int64_t)(tb + a) * C + c] = from_f32<TOut>(S * gelu_tanh_f(cy[a] + yb));
+        }
+    }
+    *sp = S;
+}
+
+// ---- linear attention with a matrix state ---------------------------------------------------------------------------------------------
+constexpr int kTile = 16;
+
+struct LinAttnArgs {
+    const float* proj; int64_t ld;
+    int off_q, off_k, off_v, off_i, off_f;      // columns of proj: q, k [H dk], v [H dv], gate pre-activations [H] (exponential gating only)
+    const float* decay;                          // [H] (fixed decay)
+    const float* i_bias; const float* f_bias;    // [H]
+    float cap, q_scale; int act;
+    float* S; float* nrm; float* mx;             // [slots, H, dv, dk], [slots, H, ceil(dv / 16), dk], [slots, H, ceil(dv / 16)]
+    float* out;                                  // [T, H dv]
+    const int32_t* cu_seqlens; const int32_t* seq_slots; const int32_t* seq_start;
+    int H, dk, dv;
+};
+
+template <int kR, bool kExp>
+__global__ void __launch_bounds__(128)
+linear_attention_kernel(const LinAttnArgs A) {
+    pdl_wait();
+    pdl_trigger();
+    constexpr int kP = 8 * kR;                   // padded key rows
+    extern __shared__ __align__(16) float smem[];
+    float* sq = smem;                            // [kTile][kP]
+    float* sk = sq + kTile * kP;                 // [kTile][kP]
+    float* sv = sk + kTile * kP;                 // [kTile][16]
+    float* sa = sv + kTile * 16;                 // [kTile] decay of the state
+    float* sb = sa + kTile;                      // [kTile] weight of the new outer product
+    float* se = sb + kTile;                      // [kTile] e^(-m_t)
+    float* sf = se + kTile;                      // [kTile] f_t, then scratch
+    float* si = sf + kTile;                      // [kTile] i_t
+    float* sm = si + kTile;                      // [kTile + 1] m before the tile's first token, then m_t
+    const int h = blockIdx.y, b = blockIdx.z;
+    const int H = A.H, dk = A.dk, dv = A.dv;
+    const int t0 = A.cu_seqlens[b], t1 = A.cu_seqlens[b + 1];
+    if (t1 <= t0) return;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int part = lane >> 2, cl = lane & 3;
+    const int colb = warp * 4 + cl;              // column inside the block's 16
+    const int col = blockIdx.x * 16 + colb;
+    const bool col_ok = col < dv;
+    const bool fresh = A.seq_start[b] == 0;
+    const int64_t slot = A.seq_slots[b];
+    float* Sp = A.S + ((slot * H + h) * dv + (col_ok ? col : 0)) * (int64_t)dk + part * kR;
+    // the normaliser and the maximum are kept once per block of 16 columns: every block reads and writes a copy of its own
+    const int64_t own = (slot * H + h) * (int64_t)gridDim.x + blockIdx.x;
+    float* np = kExp ? A.nrm + own * dk + part * kR : nullptr;
+    float S[kR], nv[kR];
+#pragma unroll
+    for (int r = 0; r < kR; ++r) {
+        const bool ok = part * kR + r < dk;
+        S[r] = (!fresh && col_ok && ok) ? Sp[r] : 0.f;
+        nv[r] = (kExp && !fresh && ok) ? np[r] : 0.f;
+    }
+    if (kExp && threadIdx.x == 0) sm[0] = fresh ? 0.f : A.mx[own];
+    const float fixed_a = kExp ? 0.f : A.decay[h];
+    for (int tb = t0; tb < t1; tb += kTile) {
+        const int nt = min(kTile, t1 - tb);
+        __syncthreads();                         // the previous tile has been walked
+        for (int e = threadIdx.x; e < nt * kP; e += 128) {
+            const int tt = e / kP, r = e - tt * kP;
+            float qv = 0.f, kv = 0.f;
+            if (r < dk) {
+                const float* row = A.proj + (int64_t)(tb + tt) * A.ld;
+                qv = row[A.off_q + h * dk + r]; kv = row[A.off_k + h * dk + r];
+                if (A.act == 1) { qv = silu_f(qv); kv = silu_f(kv); }
+                qv *= A.q_scale;
+            }
+            sq[tt * kP + r] = qv; sk[tt * kP + r] = kv;
+        }
+        for (int e = threadIdx.x; e < nt * 16; e += 128) {
+            const int tt = e >> 4, c = e & 15;
+            const int gc = blockIdx.x * 16 + c;
+            float v = 0.f;
+            if (gc < dv) { v = A.proj[(int64_t)(tb + tt) * A.ld + A.off_v + h * dv + gc]; if (A.act == 1) v = silu_f(v); }
+            sv[e] = v;
+        }
+        if (kExp && warp == 3) {
+            // gate values of the tile's tokens, the chain of maxima, then the coefficients
+            if (lane < nt) {
+                const float* row = A.proj + (int64_t)(tb + lane) * A.ld;
+                const float zi = row[A.off_i + h] + (A.i_bias ? A.i_bias[h] : 0.f), zf = row[A.off_f + h] + (A.f_bias ? A.f_bias[h] : 0.f);
+                si[lane] = A.cap * tanhf(zi / A.cap);
+                sf[lane] = log_sigmoid_f(A.cap * tanhf(zf / A.cap));
+            }
+            __syncwarp();
+            if (lane == 0) {
+                float m = sm[0];
+                for (int tt = 0; tt < nt; ++tt) { m = fmaxf(sf[tt] + m, si[tt]); sm[tt + 1] = m; }
+            }
+            __syncwarp();
+            if (lane < nt) {
+                const float m_prev = sm[lane], m_new = sm[lane + 1];
+                sa[lane] = expf(sf[lane] + m_prev - m_new);
+                sb[lane] = expf(si[lane] - m_new);
+                se[lane] = expf(-m_new);
+            }
+        }
+        __syncthreads();
+        for (int tt = 0; tt < nt; ++tt) {
+            const float a = kExp ? sa[tt] : fixed_a;
+            const float bv = (kExp ? sb[tt] : 1.0f) * sv[tt * 16 + colb];
+            const float bn = kExp ? sb[tt] : 0.f;
+            float acc = 0.f, nq = 0.f;
+            const float4* q4 = reinterpret_cast<const float4*>(sq + tt * kP + part * kR);
+            const float4* k4 = reinterpret_cast<const float4*>(sk + tt * kP + part * kR);
+#pragma unroll
+            for (int r4 = 0; r4 < kR / 4; ++r4) {
+                const float4 qq = q4[r4], kk = k4[r4];
+                const float qa[4] = {qq.x, qq.y, qq.z, qq.w}, ka[4] = {kk.x, kk.y, kk.z, kk.w};
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    const int r = r4 * 4 + j;
+                    S[r] = fmaf(a, S[r], ka[j] * bv);
+                    acc = fmaf(S[r], qa[j], acc);
+                    if (kExp) { nv[r] = fmaf(a, nv[r], ka[j] * bn); nq = fmaf(nv[r], qa[j], nq); }
+                }
+            }
+#pragma unroll
+            for (int o = 4; o < 32; o <<= 1) {
+                acc += __shfl_xor_sync(0xffffffffu, acc, o);
+                if (kExp) nq += __shfl_xor_sync(0xffffffffu, nq, o);
+            }
+            if (part == 0 && col_ok) {
+                float o = acc;
+                if (kExp) o = acc / (fmaxf(fabsf(nq), se[tt]) + 1e-6f);
+                A.out[(int64_t)(tb + tt) * H * dv + h * dv + col] = o;
+            }
+        }
+        if (kExp) {
+            __syncthreads();
+            if (threadIdx.x == 0) sm[0] = sm[nt];
+        }
+    }
+#pragma unroll
+    for (int r = 0; r < kR; ++r) {
+        const bool ok = part * kR + r < dk;
+        if (col_ok && ok) Sp[r] = S[r];
+        if (kExp && ok && warp == 0 && cl == 0) np[r] = nv[r];
+    }
+    if (kExp) {
+        __syncthreads();
+        if (threadIdx.x == 0) A.mx[own] = sm[0];
+    }
+}
+
+template <int kR, bool kExp>
+void launch_linear_attention(const LinAttnArgs& A, int num_seqs, cudaStream_t st) {
+    const int smem = (2 * kTile * 8 * kR + kTile * 16 + 6 * kTile + 1) * (int)sizeof(float);
+    ensure_dynamic_smem(reinterpret_cast<const void*>(linear_attention_kernel<kR, kExp>), smem);
+    launch_pdl(linear_attention_kernel<kR, kExp>, dim3(ceil_div(A.dv, 16), A.H, num_seqs), dim3(128), (size_t)smem, st, A);
+}
+
+template <bool kExp>
+bool dispatch_linear_attention(const LinAttnArgs& A, int num_seqs, cudaStream_t st) {
+    if (A.dk <= 32) launch_linear_attention<4, kExp>(A, num_seqs, st);
+    else if (A.dk <= 64) launch_linear_attention<8, kExp>(A, num_seqs, st);
+    else if (A.dk <= 128) launch_linear_attention<16, kExp>(A, num_seqs, st);
+    else if (A.dk <= 256) launch_linear_attention<32, kExp>(A, num_seqs, st);
+    else return false;
+    return true;
+}
+
+}  // namespace
+}  // namespace b200
+
+using namespace b200;
+
+extern "C" {
+
+void causal_conv_ex(const float* x, int64_t ldx, const float* in_bias, const float* taps, const float* out_bias, float* conv_state, void* y, int64_t ldy,
+                    const int32_t* token_seq, const int32_t* cu_seqlens, const int32_t* seq_slots, const int32_t* seq_start, int32_t num_tokens,
+                    int32_t num_seqs, int32_t channels, int32_t num_taps, int32_t act, int32_t add_input, int32_t out_dtype, int64_t stream) {
+    if (num_tokens == 0 || num_seqs == 0) return;
+    B200_REQUIRE(x && taps && conv_state && y && token_seq && cu_seqlens && seq_slots && seq_start && channels > 0 && num_taps >= 1 && ldx >= channels &&
+                 ldy >= channels && num_tokens <= 65535 && num_seqs <= 65535 && (act == 0 || act == 1), kErrBadArg, "causal_conv_ex: bad arguments");
+    cudaStream_t st = as_stream(stream);
+    const dim3 grid(ceil_div(channels, 128), num_tokens);
+    if (out_dtype == B200_F32)
+        launch_pdl(causal_conv_ex_kernel<float>, grid, dim3(128), 0, st, x, ldx, in_bias, taps, out_bias, (const float*)conv_state, (float*)y, ldy, token_seq,
+                   cu_seqlens, seq_slots, seq_start, channels, num_taps, act, add_input);
+    else if (out_dtype == B200_BF16)
+        launch_pdl(causal_conv_ex_kernel<__nv_bfloat16>, grid, dim3(128), 0, st, x, ldx, in_bias, taps, out_bias, (const float*)conv_state, (__nv_bfloat16*)y, ldy,
+                   token_seq, cu_seqlens, seq_slots, seq_start, channels, num_taps, act, add_input);
+    else { set_error(kErrUnsupported, "causal_conv_ex: out dtype %d (f32 / bf16)", out_dtype); return; }
+    count_launch();
+    if (num_taps > 1) {
+        launch_pdl(causal_conv_roll_kernel, dim3(ceil_div(channels, 128), num_seqs), dim3(128), 0, st, x, ldx, in_bias, conv_state, cu_seqlens, seq_slots, seq_start,
+                   channels, num_taps);
+        count_launch();
+    }
+    check_launch("causal_conv_ex");
+}
+
+void block_diag_linear(const float* x, int64_t ldx, const float* weight, const float* bias, float* out, int64_t ldy, int32_t num_tokens, int32_t blocks,
+                       int32_t rows_per_block, int32_t cols_per_block, int64_t stream) {
+    if (num_tokens == 0) return;
+    B200_REQUIRE(x && weight && out && blocks > 0 && blocks <= 65535 && rows_per_block > 0 && cols_per_block > 0 && ldx >= (int64_t)blocks * cols_per_block &&
+                 ldy >= (int64_t)blocks * rows_per_block, kErrBadArg, "block_diag_linear: bad arguments");
+    cudaStream_t st = as_stream(stream);
+    if (num_tokens <= 8)
+        launch_pdl(block_diag_rows_kernel, dim3(ceil_div(rows_per_block, 8), ceil_div(num_tokens, 4), blocks), dim3(256), 0, st, x, ldx, weight, bias, out, ldy,
+                   num_tokens, rows_per_block, cols_per_block);
+    else
+        launch_pdl(block_diag_linear_kernel, dim3(ceil_div(rows_per_block, kBN), ceil_div(num_tokens, kBM), blocks), dim3(256), 0, st, x, ldx, weight, bias, out, ldy,
+                   num_tokens, rows_per_block, cols_per_block);
+    count_launch();
+    check_launch("block_diag_linear");
+}
+
+void gated_linear_scan(const float* u, int64_t ldu, const float* gates, int64_t ld_gates, const float* lam, const float* y_pre, int64_t ldy, const float* y_bias,
+                       float* state, void* out, const int32_t* cu_seqlens, const int32_t* seq_slots, const int32_t* seq_start, int32_t num_seqs, int32_t channels,
+                       int32_t block_channels, float decay_scale, int32_t out_dtype, int64_t stream) {
+    if (num_seqs == 0) return;
+    B200_REQUIRE(u && gates && lam && y_pre && state && out && cu_seqlens && seq_slots && seq_start && channels > 0 && block_channels > 0 &&
+                 channels % block_channels == 0 && ldu >= channels && ldy >= channels && ld_gates >= 2 * (int64_t)channels && num_seqs <= 65535, kErrBadArg,
+                 "gated_linear_scan: bad arguments");
+    cudaStream_t st = as_stream(stream);
+    const dim3 grid(ceil_div(channels, 64), num_seqs);
+    if (out_dtype == B200_F32)
+        launch_pdl(gated_linear_scan_kernel<float>, grid, dim3(64), 0, st, u, ldu, gates, ld_gates, lam, y_pre, ldy, y_bias, state, (float*)out, cu_seqlens, seq_slots,
+                   seq_start, channels, block_channels, decay_scale);
+    else if (out_dtype == B200_BF16)
+        launch_pdl(gated_linear_scan_kernel<__nv_bfloat16>, grid, dim3(64), 0, st, u, ldu, gates, ld_gates, lam, y_pre, ldy, y_bias, state, (__nv_bfloat16*)out,
+                   cu_seqlens, seq_slots, seq_start, channels, block_channels, decay_scale);
+    else { set_error(kErrUnsupported, "gated_linear_scan: out dtype %d (f32 / bf16)", out_dtype); return; }
+    count_launch();
+    check_launch("gated_linear_scan");
+}
+
+void linear_attention(const float* proj, int64_t ld, int32_t off_q, int32_t off_k, int32_t off_v, int32_t off_i, int32_t off_f, const float* decay,
+                      const float* i_bias, const float* f_bias, float gate_cap, float q_scale, int32_t act, int32_t gating, float* state, float* normaliser,
+                      float* maximum, float* out, const int32_t* cu_seqlens, const int32_t* seq_slots, const int32_t* seq_start, int32_t num_seqs,
+                      int32_t num_heads, int32_t dk, int32_t dv, int64_t stream) {
+    if (num_seqs == 0) return;
+    B200_REQUIRE(proj && state && out && cu_seqlens && seq_slots && seq_start && num_heads > 0 && num_heads <= 65535 && num_seqs <= 65535 && dk > 0 && dv > 0 &&
+                 (act == 0 || act == 1) && (gating == 0 || gating == 1), kErrBadArg, "linear_attention: bad arguments");
+    B200_REQUIRE(gating == 0 ? decay != nullptr : (normaliser && maximum && gate_cap > 0.f), kErrBadArg,
+                 "linear_attention: fixed decay needs decay[H]; exponential gating needs the normaliser, the maximum and a positive cap");
+    B200_REQUIRE(dk <= 256, kErrUnsupported, "linear_attention: key size %d > 256", dk);
+    LinAttnArgs A{proj, ld, off_q, off_k, off_v, off_i, off_f, decay, i_bias, f_bias, gate_cap, q_scale, act, state, normaliser, maximum, out,
+                  cu_seqlens, seq_slots, seq_start, num_heads, dk, dv};
+    cudaStream_t st = as_stream(stream);
+    if (gating == 0) dispatch_linear_attention<false>(A, num_seqs, st);
+    else dispatch_linear_attention<true>(A, num_seqs, st);
+    count_launch();
+    check_launch("linear_attention");
+}
+
+}  // extern "C"

@@ -6,8 +6,10 @@
 //                     outputs form `groups` equal runs of neighbours, a group's score is its best choice score, and only members of the
 //                     `keep` best groups can be chosen (the others count as -inf); the `top` best choice scores are taken (ties: the lower
 //                     index); weights = s of the chosen / (their sum + 1e-20) * scale.  groups <= 1 switches the restriction off.
-//   moe_gate_up       act[p] = silu(W_gate[e] h) * (W_up[e] h) for pair p = (token, choice) with expert e < E; outputs e >= E are identity
-//                     experts (no weights) and are skipped.
+//                     The _ex form takes the scores from a sigmoid per output instead of the softmax, and may leave the chosen scores as they are.
+//   moe_gate_up       act[p] = silu(W_gate[e] h) * (W_up[e] h); the _ex form may first multiply both products by the pair's weight (an expert fed its
+//                     token times the router's score) and has the clamped activation of glu_packed.  Pair p = (token, choice) with expert e < E; outputs
+//                     e >= E are identity experts (no weights) and are skipped.
 //   moe_down          y[row] = W_down[e] act[p] for the pairs in expert order (moe_align with tiles of one row);
 //   moe_combine_rows  out[t] = sum over the token's choices, in choice order, of weight * y[row of the pair], or weight * x[t] for an
 //                     identity expert.
@@ -21,7 +23,7 @@ namespace {
 
 __global__ void __launch_bounds__(32)
 moe_route_kernel(const float* __restrict__ logits, int64_t ld, const float* __restrict__ correction, int32_t* __restrict__ ids, float* __restrict__ weights,
-                 int N, int top, int groups, int keep, float scale) {
+                 int N, int top, int groups, int keep, float scale, int score_fn, int normalise) {
     pdl_wait();
     pdl_trigger();
     extern __shared__ float sm[];
@@ -30,14 +32,18 @@ moe_route_kernel(const float* __restrict__ logits, int64_t ld, const float* __re
     float* gbest = sm + 2 * N;     // [groups]
     const int t = blockIdx.x, lane = threadIdx.x;
     const float* z = logits + (int64_t)t * ld;
-    float mx = -INFINITY;
-    for (int i = lane; i < N; i += 32) mx = fmaxf(mx, z[i]);
-    mx = warp_max(mx);
-    float sum = 0.f;
-    for (int i = lane; i < N; i += 32) { const float e = expf(z[i] - mx); s[i] = e; sum += e; }
-    sum = warp_sum(sum);
-    const float inv = 1.0f / sum;
-    for (int i = lane; i < N; i += 32) { s[i] *= inv; pick[i] = s[i] + (correction ? correction[i] : 0.f); }
+    if (score_fn == 1) {
+        for (int i = lane; i < N; i += 32) { s[i] = 1.0f / (1.0f + expf(-z[i])); pick[i] = s[i] + (correction ? correction[i] : 0.f); }
+    } else {
+        float mx = -INFINITY;
+        for (int i = lane; i < N; i += 32) mx = fmaxf(mx, z[i]);
+        mx = warp_max(mx);
+        float sum = 0.f;
+        for (int i = lane; i < N; i += 32) { const float e = expf(z[i] - mx); s[i] = e; sum += e; }
+        sum = warp_sum(sum);
+        const float inv = 1.0f / sum;
+        for (int i = lane; i < N; i += 32) { s[i] *= inv; pick[i] = s[i] + (correction ? correction[i] : 0.f); }
+    }
     __syncwarp();
     if (groups > 1) {
         const int per = N / groups;
@@ -74,7 +80,7 @@ moe_route_kernel(const float* __restrict__ logits, int64_t ld, const float* __re
         wsum += s[bi];
         __syncwarp();
     }
-    const float norm = scale / (wsum + 1e-20f);
+    const float norm = normalise ? scale / (wsum + 1e-20f) : scale;
     for (int r = lane; r < top; r += 32) weights[(int64_t)t * top + r] = s[ids[(int64_t)t * top + r]] * norm;
 }
 
@@ -115,7 +121,7 @@ constexpr int kDownCols = 64;      // output columns per block of moe_down
 template <typename T>
 __global__ void __launch_bounds__(128)
 moe_gate_up_kernel(const T* __restrict__ h, int64_t ldh, const T* __restrict__ w_gu, const int32_t* __restrict__ ids, const int32_t* __restrict__ order,
-                   T* __restrict__ act, int top, int E, int ff, int D) {
+                   T* __restrict__ act, int top, int E, int ff, int D, int act_fn, float limit, const float* __restrict__ pair_scale) {
     pdl_wait();
     pdl_trigger();
     extern __shared__ float hs[];                          // [D]
@@ -133,7 +139,17 @@ moe_gate_up_kernel(const T* __restrict__ h, int64_t ldh, const T* __restrict__ w
     for (int j = blockIdx.y * kGuRows + warp; j < j1; j += 4) {
         float a = row_dot<T>(wg + (int64_t)j * D, hs, D, lane, vec), b = row_dot<T>(wg + (int64_t)(ff + j) * D, hs, D, lane, vec);
         a = warp_sum(a); b = warp_sum(b);
-        if (lane == 0) act[p * ff + j] = from_f32<T>(a / (1.0f + expf(-a)) * b);
+        if (lane == 0) {
+            if (pair_scale) { const float sc = pair_scale[p]; a *= sc; b *= sc; }         // the expert sees its token times the pair's weight
+            float v;
+            if (act_fn == 2) {
+                a = fminf(a, limit); b = fminf(fmaxf(b, -limit), limit);
+                v = a / (1.0f + expf(-1.702f * a)) * (b + 1.0f);
+            } else {
+                v = a / (1.0f + expf(-a)) * b;
+            }
+            act[p * ff + j] = from_f32<T>(v);
+        }
     }
 }
 
@@ -229,7 +245,7 @@ moe_combine_rows_kernel(const float* __restrict__ y, const int32_t* __restrict__
         float tot = 0.f;
         for (int k = 0; k < top; ++k) {
             const int row = pair_row[t * top + k];
-            tot = fmaf(weights[t * top + k], row >= 0 ? y[(int64_t)row * D + d] : x[t * ldx + d], tot);
+            tot = fmaf(weights ? weights[t * top + k] : 1.0f, row >= 0 ? y[(int64_t)row * D + d] : x[t * ldx + d], tot);
         }
         out[t * D + d] = tot;
     }
@@ -244,20 +260,32 @@ extern "C" {
 
 void moe_route(const float* logits, int64_t ld, const float* correction, int32_t* ids, float* weights, int32_t num_tokens, int32_t num_outputs, int32_t top,
                int32_t groups, int32_t keep, float scale, int64_t stream) {
+    moe_route_ex(logits, ld, correction, ids, weights, num_tokens, num_outputs, top, groups, keep, scale, 0, 1, stream);
+}
+
+void moe_route_ex(const float* logits, int64_t ld, const float* correction, int32_t* ids, float* weights, int32_t num_tokens, int32_t num_outputs, int32_t top,
+                  int32_t groups, int32_t keep, float scale, int32_t score_fn, int32_t normalise, int64_t stream) {
     if (num_tokens == 0) return;
     B200_REQUIRE(logits && ids && weights && num_outputs > 0 && top > 0 && top <= num_outputs && ld >= num_outputs, kErrBadArg, "moe_route: bad arguments");
     B200_REQUIRE(groups <= 1 || (num_outputs % groups == 0 && keep > 0 && keep <= groups), kErrBadArg, "moe_route: %d outputs do not form %d equal groups (keep %d)",
                  num_outputs, groups, keep);
     B200_REQUIRE(num_outputs <= 8192, kErrUnsupported, "moe_route: more than 8192 router outputs");
     const size_t smem = ((size_t)2 * num_outputs + (groups > 1 ? groups : 1)) * sizeof(float);
-    launch_pdl(moe_route_kernel, dim3(num_tokens), dim3(32), smem, as_stream(stream), logits, ld, correction, ids, weights, num_outputs, top, groups, keep, scale);
+    launch_pdl(moe_route_kernel, dim3(num_tokens), dim3(32), smem, as_stream(stream), logits, ld, correction, ids, weights, num_outputs, top, groups, keep, scale,
+               score_fn, normalise);
     count_launch();
     check_launch("moe_route");
 }
 
 void moe_gate_up(const void* h, int64_t ldh, const void* w_gate_up, const int32_t* ids, const int32_t* order, void* act, int32_t num_tokens, int32_t top,
                  int32_t num_experts, int32_t ff, int32_t width, int32_t dtype, int64_t stream) {
+    moe_gate_up_ex(h, ldh, w_gate_up, ids, order, act, num_tokens, top, num_experts, ff, width, 0, 0.f, nullptr, dtype, stream);
+}
+
+void moe_gate_up_ex(const void* h, int64_t ldh, const void* w_gate_up, const int32_t* ids, const int32_t* order, void* act, int32_t num_tokens, int32_t top,
+                    int32_t num_experts, int32_t ff, int32_t width, int32_t act_fn, float limit, const float* pair_scale, int32_t dtype, int64_t stream) {
     if (num_tokens == 0 || num_experts == 0) return;
+    B200_REQUIRE(act_fn == 0 || act_fn == 2, kErrBadArg, "moe_gate_up: activation %d (0 = SiLU, 2 = clamped)", act_fn);
     B200_REQUIRE(h && w_gate_up && ids && act && top > 0 && ff > 0 && width > 0 && width <= 16384 && ldh >= width, kErrBadArg, "moe_gate_up: bad arguments");
     cudaStream_t st = as_stream(stream);
     const dim3 grid((unsigned)((int64_t)num_tokens * top), (unsigned)((ff + kGuRows - 1) / kGuRows));
@@ -265,10 +293,11 @@ void moe_gate_up(const void* h, int64_t ldh, const void* w_gate_up, const int32_
     ensure_dynamic_smem(reinterpret_cast<const void*>(moe_gate_up_kernel<float>), (int)smem);
     ensure_dynamic_smem(reinterpret_cast<const void*>(moe_gate_up_kernel<__nv_bfloat16>), (int)smem);
     if (dtype == B200_F32)
-        launch_pdl(moe_gate_up_kernel<float>, grid, dim3(128), smem, st, (const float*)h, ldh, (const float*)w_gate_up, ids, order, (float*)act, top, num_experts, ff, width);
+        launch_pdl(moe_gate_up_kernel<float>, grid, dim3(128), smem, st, (const float*)h, ldh, (const float*)w_gate_up, ids, order, (float*)act, top, num_experts, ff, width,
+                   act_fn, limit, pair_scale);
     else if (dtype == B200_BF16)
         launch_pdl(moe_gate_up_kernel<__nv_bfloat16>, grid, dim3(128), smem, st, (const __nv_bfloat16*)h, ldh, (const __nv_bfloat16*)w_gate_up, ids, order,
-                   (__nv_bfloat16*)act, top, num_experts, ff, width);
+                   (__nv_bfloat16*)act, top, num_experts, ff, width, act_fn, limit, pair_scale);
     else { set_error(kErrUnsupported, "moe_gate_up: dtype %d (f32 / bf16)", dtype); return; }
     count_launch();
     check_launch("moe_gate_up");
@@ -333,7 +362,7 @@ void silu_mul_packed(const float* gate_up, void* out, int64_t rows, int32_t ff, 
 void moe_combine_rows(const float* y, const int32_t* pair_row, const float* weights, const float* x, int64_t ldx, float* out, int32_t num_tokens, int32_t top,
                       int32_t width, int64_t stream) {
     if (num_tokens == 0) return;
-    B200_REQUIRE(y && pair_row && weights && x && out && top > 0 && width > 0 && ldx >= width, kErrBadArg, "moe_combine_rows: bad arguments");
+    B200_REQUIRE(y && pair_row && x && out && top > 0 && width > 0 && ldx >= width, kErrBadArg, "moe_combine_rows: bad arguments");
     launch_pdl(moe_combine_rows_kernel, dim3(num_tokens), dim3(256), 0, as_stream(stream), y, pair_row, weights, x, ldx, out, top, width);
     count_launch();
     check_launch("moe_combine_rows");

@@ -10,6 +10,15 @@
 //   residual_rms_norm  the two closing forms of a sublayer on the f32 stream x, in place: mode 0 "norm after the sum"
 //                    x <- norm(alpha x + y) * w, mode 1 x <- x + norm(y) * w; optionally also x in 16 bits for the next product;
 //   gelu_tanh_gather_mul  out[t, i] = gelu_tanh(z[t, i]) * table[ids[t], col0 + i] (a per-token embedding gated by the stream).
+//   embedding_positional  out[t] = table[ids[t]] * scale + pos_table[positions[t]] (a learned position vector per place);
+//   layer_norm_ex    out[r] = (x[src(r)] - mean) / sqrt(var + eps) * w + b with the biased variance, in up to two copies: one of the
+//                    compute dtype for the next product, one f32 for whatever else reads the normed row;
+//   gated_residual_add  x <- x + sigmoid(z + bias) * y, the gate's pre-activation z being a product of its own (z null: x <- x + y);
+//   glu_packed       out = act(gate) * up from a packed [rows, 2 ff] product, act one of silu, tanh GELU, or the clamped form
+//                    g' = min(g, limit), u' = clamp(u, +-limit), g' sigmoid(1.702 g') (u' + 1); a per-row factor may multiply gate and
+//                    up first (an expert that sees its token times the router's score);
+//   group_rms_norm_gate  out = o / rms(o over a group of neighbours) * w * act(gate): the closing norm of the linear-attention mixers,
+//                    one group per head or one for the whole row.
 // Any row length (no vector-width rule): the rows these models use are a few hundred to a few thousand floats and every kernel
 // here is one pass over them from L2.
 #include "common.cuh"
@@ -152,6 +161,110 @@ __global__ void gelu_tanh_gather_mul_kernel(const float* __restrict__ z, int64_t
     out[i] = from_f32<TOut>(gelu_tanh_f(z[r * ldz + c]) * to_f32<TTab>(table[(int64_t)id * ld_table + col0 + c]));
 }
 
+
+template <typename TTab>
+__global__ void embedding_positional_kernel(const TTab* __restrict__ table, const TTab* __restrict__ pos_table, const int32_t* __restrict__ ids,
+                                            const int32_t* __restrict__ positions, float* __restrict__ out, int dim, int vocab, int max_pos, float scale) {
+    pdl_wait();
+    pdl_trigger();
+    const int t = blockIdx.x;
+    int id = ids[t];
+    id = id < 0 ? 0 : (id >= vocab ? vocab - 1 : id);
+    int p = positions[t];
+    p = p < 0 ? 0 : (p >= max_pos ? max_pos - 1 : p);
+    for (int i = threadIdx.x; i < dim; i += blockDim.x)
+        out[(int64_t)t * dim + i] = fmaf(to_f32<TTab>(table[(int64_t)id * dim + i]), scale, to_f32<TTab>(pos_table[(int64_t)p * dim + i]));
+}
+
+template <typename TOut>
+__global__ void __launch_bounds__(256)
+layer_norm_ex_kernel(const float* __restrict__ x, const float* __restrict__ w, const float* __restrict__ b, TOut* out, float* out32,
+                     const int32_t* __restrict__ row_index, int n, int64_t ldx, float eps) {
+    pdl_wait();
+    pdl_trigger();
+    __shared__ float red[8];
+    const int row = blockIdx.x;
+    const int64_t src = row_index ? row_index[row] : row;
+    const float* xr = x + src * ldx;
+    float s = 0.f;
+    for (int i = threadIdx.x; i < n; i += 256) s += xr[i];
+    const float mean = block_sum_256(s, red) / (float)n;
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < n; i += 256) { const float d = xr[i] - mean; ss = fmaf(d, d, ss); }
+    const float sc = 1.0f / sqrtf(block_sum_256(ss, red) / (float)n + eps);
+    for (int i = threadIdx.x; i < n; i += 256) {
+        const float v = fmaf((xr[i] - mean) * sc, w[i], b ? b[i] : 0.f);
+        if (out) out[(int64_t)row * n + i] = from_f32<TOut>(v);
+        if (out32) out32[(int64_t)row * n + i] = v;
+    }
+}
+
+__global__ void gated_residual_add_kernel(float* __restrict__ x, const float* __restrict__ y, int64_t ldy, const float* __restrict__ z, int64_t ldz,
+                                          const float* __restrict__ bias, int64_t rows, int n) {
+    pdl_wait();
+    pdl_trigger();
+    const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= rows * n) return;
+    const int64_t r = i / n;
+    const int c = (int)(i - r * n);
+    float v = y[r * ldy + c];
+    if (z) v *= 1.0f / (1.0f + expf(-(z[r * ldz + c] + (bias ? bias[c] : 0.f))));
+    x[i] += v;
+}
+
+__device__ __forceinline__ float glu_value(float g, float u, int act, float limit) {
+    if (act == 0) return g / (1.0f + expf(-g)) * u;
+    if (act == 1) return gelu_tanh_f(g) * u;
+    g = fminf(g, limit);
+    u = fminf(fmaxf(u, -limit), limit);
+    return g / (1.0f + expf(-1.702f * g)) * (u + 1.0f);
+}
+
+template <typename TOut>
+__global__ void glu_packed_kernel(const float* __restrict__ gu, TOut* __restrict__ out, int64_t rows, int ff, int64_t ld, int act, float limit,
+                                  const float* __restrict__ row_scale, const int32_t* __restrict__ scale_index) {
+    pdl_wait();
+    pdl_trigger();
+    const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= rows * ff) return;
+    const int64_t r = i / ff;
+    const int c = (int)(i - r * ff);
+    float g = gu[r * ld + c], u = gu[r * ld + ff + c];
+    if (row_scale) {
+        const int64_t j = scale_index ? scale_index[r] : r;
+        if (j < 0) { out[i] = from_f32<TOut>(0.f); return; }          // a padding row of a sorted, tiled order
+        const float s = row_scale[j];
+        g *= s; u *= s;
+    }
+    out[i] = from_f32<TOut>(glu_value(g, u, act, limit));
+}
+
+template <typename TOut>
+__global__ void __launch_bounds__(128)
+group_rms_norm_gate_kernel(const float* __restrict__ o, int64_t ldo, const float* __restrict__ w, const float* __restrict__ gate, int64_t ldg, TOut* __restrict__ out,
+                           int n, int glen, float eps, int gate_act) {
+    pdl_wait();
+    pdl_trigger();
+    __shared__ float red[4];
+    const int64_t t = blockIdx.y;
+    const int c0 = blockIdx.x * glen;
+    const float* orow = o + t * ldo + c0;
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < glen; i += 128) { const float v = orow[i]; ss = fmaf(v, v, ss); }
+    ss = warp_sum(ss);
+    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = ss;
+    __syncthreads();
+    const float sc = 1.0f / sqrtf((red[0] + red[1] + red[2] + red[3]) / (float)glen + eps);
+    for (int i = threadIdx.x; i < glen; i += 128) {
+        float v = orow[i] * sc * (w ? w[c0 + i] : 1.0f);
+        if (gate) {
+            const float z = gate[t * ldg + c0 + i];
+            v *= gate_act == 0 ? 1.0f / (1.0f + expf(-z)) : z / (1.0f + expf(-z));
+        }
+        out[t * n + c0 + i] = from_f32<TOut>(v);
+    }
+}
+
 }  // namespace
 }  // namespace b200
 
@@ -242,6 +355,76 @@ void gelu_tanh_gather_mul(const float* z, int64_t ldz, const void* table, int64_
                    ids, (__nv_bfloat16*)out, (int64_t)rows, dim, vocab);
     count_launch();
     check_launch("gelu_tanh_gather_mul");
+}
+
+void embedding_positional(const void* table, const void* pos_table, const int32_t* ids, const int32_t* positions, float* out, int32_t num_tokens, int32_t dim,
+                          int32_t vocab, int32_t max_pos, float scale, int32_t table_dtype, int64_t stream) {
+    if (num_tokens == 0) return;
+    B200_REQUIRE(table && pos_table && ids && positions && out && dim > 0 && vocab > 0 && max_pos > 0, kErrBadArg, "embedding_positional: bad arguments");
+    cudaStream_t st = as_stream(stream);
+    if (table_dtype == B200_F32)
+        launch_pdl(embedding_positional_kernel<float>, dim3(num_tokens), dim3(128), 0, st, (const float*)table, (const float*)pos_table, ids, positions, out, dim, vocab,
+                   max_pos, scale);
+    else if (table_dtype == B200_BF16)
+        launch_pdl(embedding_positional_kernel<__nv_bfloat16>, dim3(num_tokens), dim3(128), 0, st, (const __nv_bfloat16*)table, (const __nv_bfloat16*)pos_table, ids,
+                   positions, out, dim, vocab, max_pos, scale);
+    else { set_error(kErrUnsupported, "embedding_positional: table dtype %d (f32 / bf16)", table_dtype); return; }
+    count_launch();
+    check_launch("embedding_positional");
+}
+
+void layer_norm_ex(const float* x, const float* weight, const float* bias, void* out, float* out32, const int32_t* row_index, int32_t rows, int32_t n, int64_t ldx,
+                   float eps, int32_t out_dtype, int64_t stream) {
+    if (rows == 0) return;
+    B200_REQUIRE(x && weight && (out || out32) && rows > 0 && n > 0 && ldx >= n, kErrBadArg, "layer_norm_ex: bad arguments");
+    cudaStream_t st = as_stream(stream);
+    if (out_dtype == B200_F32) launch_pdl(layer_norm_ex_kernel<float>, dim3(rows), dim3(256), 0, st, x, weight, bias, (float*)out, out32, row_index, n, ldx, eps);
+    else if (out_dtype == B200_BF16)
+        launch_pdl(layer_norm_ex_kernel<__nv_bfloat16>, dim3(rows), dim3(256), 0, st, x, weight, bias, (__nv_bfloat16*)out, out32, row_index, n, ldx, eps);
+    else { set_error(kErrUnsupported, "layer_norm_ex: out dtype %d (f32 / bf16)", out_dtype); return; }
+    count_launch();
+    check_launch("layer_norm_ex");
+}
+
+void gated_residual_add(float* x, const float* y, int64_t ldy, const float* gate_logits, int64_t ld_gate, const float* gate_bias, int32_t rows, int32_t n,
+                        int64_t stream) {
+    if (rows == 0) return;
+    B200_REQUIRE(x && y && rows > 0 && n > 0 && ldy >= n && (!gate_logits || ld_gate >= n), kErrBadArg, "gated_residual_add: bad arguments");
+    const unsigned grid = (unsigned)(((int64_t)rows * n + 255) / 256);
+    launch_pdl(gated_residual_add_kernel, dim3(grid), dim3(256), 0, as_stream(stream), x, y, ldy, gate_logits, ld_gate, gate_bias, (int64_t)rows, n);
+    count_launch();
+    check_launch("gated_residual_add");
+}
+
+void glu_packed(const float* gate_up, void* out, int64_t rows, int32_t ff, int64_t ld, int32_t act, float limit, const float* row_scale, const int32_t* scale_index,
+                int32_t out_dtype, int64_t stream) {
+    if (rows == 0 || ff == 0) return;
+    B200_REQUIRE(gate_up && out && rows > 0 && ff > 0 && ld >= 2 * (int64_t)ff && act >= 0 && act <= 2 && (row_scale || !scale_index), kErrBadArg,
+                 "glu_packed: bad arguments");
+    const unsigned grid = (unsigned)((rows * ff + 255) / 256);
+    cudaStream_t st = as_stream(stream);
+    if (out_dtype == B200_F32) launch_pdl(glu_packed_kernel<float>, dim3(grid), dim3(256), 0, st, gate_up, (float*)out, rows, ff, ld, act, limit, row_scale, scale_index);
+    else if (out_dtype == B200_BF16)
+        launch_pdl(glu_packed_kernel<__nv_bfloat16>, dim3(grid), dim3(256), 0, st, gate_up, (__nv_bfloat16*)out, rows, ff, ld, act, limit, row_scale, scale_index);
+    else { set_error(kErrUnsupported, "glu_packed: out dtype %d (f32 / bf16)", out_dtype); return; }
+    count_launch();
+    check_launch("glu_packed");
+}
+
+void group_rms_norm_gate(const float* o, int64_t ldo, const float* weight, const float* gate, int64_t ld_gate, void* out, int32_t num_tokens, int32_t n,
+                         int32_t groups, float eps, int32_t gate_act, int32_t out_dtype, int64_t stream) {
+    if (num_tokens == 0) return;
+    B200_REQUIRE(o && out && n > 0 && groups > 0 && n % groups == 0 && ldo >= n && (!gate || ld_gate >= n) && groups <= 65535 && (gate_act == 0 || gate_act == 1),
+                 kErrBadArg, "group_rms_norm_gate: bad arguments");
+    cudaStream_t st = as_stream(stream);
+    const dim3 grid(groups, num_tokens);
+    if (out_dtype == B200_F32)
+        launch_pdl(group_rms_norm_gate_kernel<float>, grid, dim3(128), 0, st, o, ldo, weight, gate, ld_gate, (float*)out, n, n / groups, eps, gate_act);
+    else if (out_dtype == B200_BF16)
+        launch_pdl(group_rms_norm_gate_kernel<__nv_bfloat16>, grid, dim3(128), 0, st, o, ldo, weight, gate, ld_gate, (__nv_bfloat16*)out, n, n / groups, eps, gate_act);
+    else { set_error(kErrUnsupported, "group_rms_norm_gate: out dtype %d (f32 / bf16)", out_dtype); return; }
+    count_launch();
+    check_launch("group_rms_norm_gate");
 }
 
 }  // extern "C"

@@ -4,13 +4,19 @@ kernels of ``seq_ops``.  Sizes and constants are constructor arguments so that a
   GatedDeltaMixer      short causal convolution + SiLU on q / k / v, unit-norm q and k, gated delta rule over an f32 state, per-head
                        RMS norm times a SiLU gate, output projection (csrc/gated_delta.cu)
   PagedAttentionMixer  grouped-query attention over the paged cache with optional whole-row q / k RMS norm, partial rotary with
-                       optional YaRN scaling, and a chunk and / or sliding-window mask (csrc/attention_varlen.cu)
-  GatedMlp             down(act(gate x) * (up x)) with the tanh GELU (csrc/norm_act.cu)
+                       optional YaRN scaling, a chunk and / or sliding-window mask, an optional query temperature, values cached at unit
+                       root mean square, and one sigmoid gate per head (csrc/attention_varlen.cu)
+  GatedMlp             down(act(gate x) * (up x)) with the tanh GELU or SiLU (csrc/norm_act.cu)
   LatentAttentionMixer attention over a cached low-rank latent plus one shared rotated key part, softmax sink, sigmoid head gates, optionally
                        over another layer's cache (csrc/latent_attention.cu)
   RoutedExperts        softmax-routed mixture of SiLU experts: group-limited top-k with a choice-only correction, identity experts
                        (csrc/moe_ragged.cu)
   TokenSideInput       a per-token embedding gated by the stream and added back through a norm
+  GatedLinearRecurrence  two branches: gelu(W_y h) and a short convolution of W_x h run through a per-channel recurrence whose decay and
+                       input gates are block-diagonal maps of the convolved branch (csrc/linear_recurrence.cu)
+  DecayLinearAttention linear attention over an f32 matrix state with one fixed decay per head, SiLU on q / k / v, all heads normed together, sigmoid gate
+  MatrixMemoryMixer    linear attention with exponential input / forget gates held stable by a running maximum, a normaliser vector, per-head norm
+  ParallelMixer        two mixers side by side on one input (one fused projection), half the sum of their normed outputs
 
 Activations that feed a matrix product are of the model's compute dtype (bf16 or f32); products come back in f32 and everything
 between them (norms, convolution, recurrence, softmax) is 32-bit.
@@ -82,16 +88,23 @@ class GatedDeltaMixer:
 
 class PagedAttentionMixer:
     """weights: q [H dk, D], k [G dk, D], v [G dv, D], o [D, H dv]; optional q.norm [H dk], k.norm [G dk] (plain weights, RMS over the whole
-    row).  rot = dict(dims, base, scaling) or None; chunk / window = 0 for none."""
+    row), optional g [H, D] (head h's output times sigmoid(g x)[h]).  rot = dict(dims, base, scaling) or None; chunk / window = 0 for none;
+    q_temp = dict(coef, every): the query at position p times 1 + coef ln(floor((p + 1) / every) + 1); value_norm: every value head is
+    cached divided by its root mean square."""
     kind = "kv"
 
     def __init__(self, w: Dict[str, torch.Tensor], heads: int, kv_heads: int, dk: int, dv: int, scale: float, eps: float, dtype: torch.dtype,
-                 rot: Optional[dict] = None, chunk: int = 0, window: int = 0, block_size: int = 64, max_pos: int = 4096):
+                 rot: Optional[dict] = None, chunk: int = 0, window: int = 0, block_size: int = 64, max_pos: int = 4096, q_temp: Optional[dict] = None,
+                 value_norm: bool = False):
         if heads % kv_heads:
             raise BackendError("PagedAttentionMixer: heads must be a multiple of kv_heads")
         self.H, self.G, self.dk, self.dv, self.scale, self.eps, self.dtype = heads, kv_heads, dk, dv, float(scale), eps, dtype
         self.chunk, self.window, self.block_size, self.rot = int(chunk), int(window), block_size, rot
-        self.w_in = torch.cat([w["q"], w["k"], w["v"]], 0).to(dtype).contiguous()
+        self.has_gate = "g" in w
+        self.off_g = heads * dk + kv_heads * (dk + dv)
+        self.w_in = torch.cat([w["q"], w["k"], w["v"]] + ([w["g"]] if self.has_gate else []), 0).to(dtype).contiguous()
+        self.q_temp = (float(q_temp["coef"]), int(q_temp["every"])) if q_temp else None
+        self.value_norm = bool(value_norm)
         self.q_norm = w["q.norm"].float().contiguous() if "q.norm" in w else None
         self.k_norm = w["k.norm"].float().contiguous() if "k.norm" in w else None
         self.w_o = w["o"].to(dtype).contiguous()
@@ -99,7 +112,7 @@ class PagedAttentionMixer:
         if self.rot_dims % 2 or self.rot_dims > dk:
             raise BackendError(f"PagedAttentionMixer: {self.rot_dims} rotary dims do not fit a head of {dk}")
         # 16-bit q for the tensor-core attention kernel (128-wide heads, 64-token blocks, bf16 cache); f32 q for the SIMT one
-        self.q_dtype = torch.bfloat16 if (dtype == torch.bfloat16 and dk == dv == 128 and block_size == 64) else torch.float32
+        self.q_dtype = torch.bfloat16 if (dtype == torch.bfloat16 and dk == dv == 128 and block_size == 64 and not self.has_gate) else torch.float32
         # steps of single tokens: the split-KV decode kernel, when chunks start on block borders and the head layout is one it takes
         self.decode_kernel = (self.q_dtype == torch.bfloat16 and self.chunk > 0 and self.chunk % block_size == 0 and heads // kv_heads in (1, 2, 4, 8))
         self._scratch = {}
@@ -115,13 +128,21 @@ class PagedAttentionMixer:
     def cache_shape(self):
         return (self.G, self.dk, self.dv)
 
-    def forward(self, h: torch.Tensor, batch: StepBatch, cache) -> torch.Tensor:
+    def forward(self, h: torch.Tensor, batch: StepBatch, cache, proj: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """``proj``: the product of ``w_in`` with the input when the caller has it already (columns of a wider fused projection)"""
         k_cache, v_cache = cache
         if self.rot and batch.max_position >= self.cos.shape[0]:
             self.ensure_positions(max(2 * self.cos.shape[0], batch.max_position + 1))
-        proj = ops.linear(h, self.w_in)
+        if proj is None:
+            proj = ops.linear(h, self.w_in)
         q = ops.qk_norm_rope_cache(proj, self.q_norm, self.k_norm, self.cos, self.sin, batch, k_cache, v_cache, self.H, self.G, self.dk, self.dv,
-                                   self.rot_dims, self.eps, self.q_dtype)
+                                   self.rot_dims, self.eps, self.q_dtype, q_temp=self.q_temp, v_unit_rms=self.value_norm)
+        if self.has_gate:
+            # the head outputs stay f32 until the gate has been applied, then take the compute dtype once
+            a = ops.paged_attention_varlen(q, k_cache, v_cache, batch, self.H, self.G, self.dk, self.dv, self.block_size, self.scale, self.chunk,
+                                           self.window, torch.float32)
+            a = ops.latent_out_gate(a.view(-1, self.H, self.dv), None, proj[:, self.off_g:], self.H, self.dv, self.dv, self.dtype)
+            return ops.linear(a, self.w_o)
         if self.decode_kernel and batch.pure_decode and batch.num_seqs <= 256:
             a = ops.paged_attention_decode_chunked(q, k_cache, v_cache, batch, self.H, self.G, self.dk, self.block_size, self.scale, self.chunk, self._scratch)
         else:
@@ -131,15 +152,22 @@ class PagedAttentionMixer:
 
 
 class GatedMlp:
-    """down(gelu_tanh(gate x) * (up x)); gate, up [ff, D], down [D, ff]."""
+    """down(act(gate x) * (up x)), act the tanh GELU or SiLU; gate, up [ff, D], down [D, ff]."""
 
-    def __init__(self, w: Dict[str, torch.Tensor], dtype: torch.dtype):
-        self.dtype = dtype
+    def __init__(self, w: Dict[str, torch.Tensor], dtype: torch.dtype, act: str = "gelu_tanh"):
+        if act not in ("gelu_tanh", "silu"):
+            raise BackendError(f"GatedMlp: unknown activation {act!r}")
+        self.dtype, self.act = dtype, act
         self.w_in = torch.cat([w["gate"], w["up"]], 0).to(dtype).contiguous()
         self.w_down = w["down"].to(dtype).contiguous()
 
-    def forward(self, h: torch.Tensor) -> torch.Tensor:
-        return ops.linear(ops.gelu_tanh_mul(ops.linear(h, self.w_in), self.dtype), self.w_down)
+    def forward(self, h: torch.Tensor, proj: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """``proj``: the product of ``w_in`` with the input when the caller has it already (columns of a wider fused projection)"""
+        if proj is None:
+            proj = ops.linear(h, self.w_in)
+        if self.act == "gelu_tanh":
+            return ops.linear(ops.gelu_tanh_mul(proj, self.dtype), self.w_down)
+        return ops.linear(ops.glu_packed(proj, self.act, self.dtype), self.w_down)
 
 
 GROUPED_MIN_ROWS = 256        # token-choice pairs from which the expert products take 128-row tiles per expert (below: 32-row tiles, weights on the 128-row side)
@@ -249,10 +277,18 @@ class RoutedExperts:
     """Mixture of experts with a softmax router: down(silu(gate x) * (up x)) per expert, weights e<j>.gate / e<j>.up [ff, D], e<j>.down [D, ff],
     router [N, D], optional correction [N] (added to the scores for the choice only).  N = experts + identity: the last ``identity`` router outputs
     are experts without weights whose output is the input itself.  ``groups`` / ``keep`` restrict the choice to the best groups of neighbouring
-    outputs (0 = off); the chosen scores are normalised and multiplied by ``scale`` (csrc/moe_ragged.cu)."""
+    outputs (0 = off); the chosen scores are normalised and multiplied by ``scale`` (csrc/moe_ragged.cu).
 
-    def __init__(self, w: Dict[str, torch.Tensor], experts: int, identity: int, top: int, scale: float, dtype: torch.dtype, groups: int = 0, keep: int = 0):
+    ``score`` "sigmoid" scores every output by itself; ``normalise`` False keeps the chosen scores as they are; ``weight_input`` feeds an expert its token
+    times the score instead of scaling what the expert returns; ``act`` "clamped" is g' sigmoid(1.702 g') (u' + 1) with g' = min(g, limit), u' = clamp(u,
+    +-limit)."""
+
+    def __init__(self, w: Dict[str, torch.Tensor], experts: int, identity: int, top: int, scale: float, dtype: torch.dtype, groups: int = 0, keep: int = 0,
+                 score: str = "softmax", normalise: bool = True, weight_input: bool = False, act: str = "silu", limit: float = 0.0):
         self.E, self.I, self.top, self.scale, self.groups, self.keep, self.dtype = experts, identity, top, float(scale), int(groups), int(keep), dtype
+        if score not in ("softmax", "sigmoid") or act not in ("silu", "clamped") or (weight_input and identity):
+            raise BackendError(f"RoutedExperts: score {score!r} / activation {act!r} / weighted input with identity experts")
+        self.score, self.normalise, self.weight_input, self.act, self.limit = score, bool(normalise), bool(weight_input), act, float(limit)
         self.N = experts + identity
         if tuple(w["router"].shape)[0] != self.N:
             raise BackendError(f"RoutedExperts: the router has {w['router'].shape[0]} outputs, expected {experts} + {identity}")
@@ -270,9 +306,14 @@ class RoutedExperts:
         # steps with many rows (bf16, TMA-sized operands): pairs sorted by expert, both expert products as grouped products on the tensor-core GEMM
         self.grouped = bool(experts) and dtype == torch.bfloat16 and D % 8 == 0 and self.ff % 8 == 0 and D >= 64 and self.ff >= 64
 
-    def forward(self, h: torch.Tensor, x: torch.Tensor) -> torch.Tensor:
-        """h: the input in the compute dtype, x: the same rows in f32 (what an identity expert returns)"""
-        ids, wts = ops.moe_route(ops.linear(h, self.router), self.correction, self.top, self.groups, self.keep, self.scale)
+    def forward(self, h: torch.Tensor, x: torch.Tensor, logits: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """h: the input in the compute dtype, x: the same rows in f32 (what an identity expert returns); ``logits``: the router's product when the caller has
+        it already (columns of a wider fused projection)"""
+        if logits is None:
+            logits = ops.linear(h, self.router)
+        ids, wts = ops.moe_route(logits, self.correction, self.top, self.groups, self.keep, self.scale, self.score, self.normalise)
+        # a weight on the expert's input is applied to both of its first products (W (s h) = s W h), in f32, before the activation
+        pre, post = (wts, None) if self.weight_input else (None, wts)
         if self.grouped:
             # pairs sorted by expert into tiles of 128 rows, or of 32 while experts have few rows each (the weights then take the 128-row side of the MMA and
             # stream once per tile)
@@ -280,15 +321,18 @@ class RoutedExperts:
             pair_row, row_pair, tile_expert = ops.moe_sorted_rows(ids, self.E, tile)
             xg = ops.moe_gather_rows(h, row_pair, self.top)
             gu = ops.linear_grouped(xg, self.w_gu, tile_expert, torch.empty((xg.shape[0], 2 * self.ff), dtype=torch.float32, device=h.device), tile)
-            act = ops.silu_mul_packed(gu, torch.bfloat16)
+            if self.act == "silu" and pre is None:
+                act = ops.silu_mul_packed(gu, torch.bfloat16)
+            else:
+                act = ops.glu_packed(gu, self.act, torch.bfloat16, self.limit, row_scale=None if pre is None else pre.view(-1), scale_index=None if pre is None else row_pair)
             y = ops.linear_grouped(act, self.w_d, tile_expert, torch.empty((xg.shape[0], self.w_d.shape[1]), dtype=torch.float32, device=h.device), tile)
-            return ops.moe_combine_rows(y, pair_row, wts, x)
+            return ops.moe_combine_rows(y, pair_row, post, x)
         if not self.E:                                       # identity experts only
             return ops.moe_combine_rows(x, torch.full((ids.numel(),), -1, dtype=torch.int32, device=ids.device), wts, x)
         # few rows: every pair streams its expert; the blocks walk the pairs expert by expert, so that those running together read the same weights
         pair_row, order, _ = ops.moe_sorted_rows(ids, self.E, tile=1)
-        act = ops.moe_gate_up(h, self.w_gu, ids, order)
-        return ops.moe_combine_rows(ops.moe_down(act, self.w_d, ids, order), pair_row, wts, x)
+        act = ops.moe_gate_up(h, self.w_gu, ids, order, self.act, self.limit, None if pre is None else pre.view(-1))
+        return ops.moe_combine_rows(ops.moe_down(act, self.w_d, ids, order), pair_row, post, x)
 
 
 class TokenSideInput:
@@ -304,3 +348,117 @@ class TokenSideInput:
     def forward(self, x: torch.Tensor, h: torch.Tensor, batch: StepBatch, out16: Optional[torch.Tensor]) -> None:
         g = ops.gelu_tanh_gather_mul(ops.linear(h, self.w_gate), self.table, self.col0, batch.tokens, self.dim)
         ops.residual_rms_norm(x, ops.linear(g, self.w_proj), self.norm, 1.0, self.eps, False, out16)
+
+
+class GatedLinearRecurrence:
+    """Recurrent block with a real-gated linear recurrent unit.  weights: y, x [C, D] with biases y.b, x.b [C]; conv [C, taps], conv.b [C]; ra, ri
+    [blocks, C / blocks, C / blocks] with biases ra.b, ri.b [blocks, C / blocks]; lam [C]; o [D, C].  With u = conv(x h + x.b) + conv.b, per block r =
+    sigmoid(ra u + ra.b), i = sigmoid(ri u + ri.b); S <- a S + sqrt(1 - a^2) i u with a = exp(-decay_scale r softplus(lam)); out = o (S * gelu_tanh(y h + y.b)).
+    The gates and the recurrence are f32 whatever the compute dtype."""
+    kind = "state"
+
+    def __init__(self, w: Dict[str, torch.Tensor], blocks: int, taps: int, dtype: torch.dtype, decay_scale: float = 8.0):
+        C = w["x"].shape[0]
+        if C % blocks or tuple(w["ra"].shape) != (blocks, C // blocks, C // blocks) or tuple(w["conv"].shape) != (C, taps):
+            raise BackendError(f"GatedLinearRecurrence: {C} channels in {blocks} blocks, gates {tuple(w['ra'].shape)}, convolution {tuple(w['conv'].shape)}")
+        self.C, self.blocks, self.n, self.taps, self.dtype, self.decay_scale = C, blocks, C // blocks, taps, dtype, float(decay_scale)
+        f32 = lambda name: w[name].float().contiguous() if name in w else None
+        self.w_in = torch.cat([w["y"], w["x"]], 0).to(dtype).contiguous()
+        self.y_bias, self.x_bias, self.conv, self.conv_bias, self.lam = f32("y.b"), f32("x.b"), f32("conv"), f32("conv.b"), f32("lam")
+        self.w_gates = torch.cat([w["ra"], w["ri"]], 1).float().contiguous()                        # [blocks, 2 n, n]: recurrence gate rows, then input gate rows
+        self.gate_bias = torch.cat([w["ra.b"], w["ri.b"]], 1).float().contiguous() if "ra.b" in w else None
+        self.w_o = w["o"].to(dtype).contiguous()
+
+    def state_shapes(self):
+        return ((max(self.taps - 1, 1), self.C), (self.C,))
+
+    def forward(self, h: torch.Tensor, batch: StepBatch, cache, proj: Optional[torch.Tensor] = None) -> torch.Tensor:
+        conv_state, S = cache
+        if proj is None:
+            proj = ops.linear(h, self.w_in)
+        u = ops.causal_conv(proj[:, self.C:], self.conv, conv_state, batch, in_bias=self.x_bias, out_bias=self.conv_bias)
+        gates = ops.block_diag_linear(u, self.w_gates, None if self.gate_bias is None else self.gate_bias.view(-1))
+        z = ops.gated_linear_scan(u, gates, self.lam, proj[:, :self.C], self.y_bias, S, batch, self.n, self.decay_scale, self.dtype)
+        return ops.linear(z, self.w_o)
+
+
+class DecayLinearAttention:
+    """Linear attention with one fixed decay per head: q, k = silu(W h) [H dk], v = silu(W h) [H dv]; S <- decay[h] S + k v^T, o = S^T q; the heads'
+    outputs are normed together (RMS, weight norm [H dv]), times sigmoid(g h), projected by o [D, H dv]."""
+    kind = "state"
+
+    def __init__(self, w: Dict[str, torch.Tensor], heads: int, dk: int, dv: int, decay, eps: float, dtype: torch.dtype):
+        if len(decay) != heads:
+            raise BackendError(f"DecayLinearAttention: {len(decay)} decays for {heads} heads")
+        self.H, self.dk, self.dv, self.eps, self.dtype = heads, dk, dv, eps, dtype
+        self.w_in = torch.cat([w["q"], w["k"], w["v"], w["g"]], 0).to(dtype).contiguous()
+        self.off_g = 2 * heads * dk + heads * dv
+        self.decay = torch.tensor([float(d) for d in decay], dtype=torch.float32, device=self.w_in.device)
+        self.norm = w["norm"].float().contiguous()
+        self.w_o = w["o"].to(dtype).contiguous()
+
+    def state_shapes(self):
+        return ((self.H, self.dv, self.dk),)
+
+    def forward(self, h: torch.Tensor, batch: StepBatch, cache, proj: Optional[torch.Tensor] = None) -> torch.Tensor:
+        if proj is None:
+            proj = ops.linear(h, self.w_in)
+        o = ops.linear_attention(proj, 0, self.H * self.dk, 2 * self.H * self.dk, cache[0], batch, self.H, self.dk, self.dv, act="silu", decay=self.decay)
+        z = ops.group_rms_norm_gate(o, self.norm, proj[:, self.off_g:], 1, self.eps, self.dtype)
+        return ops.linear(z, self.w_o)
+
+
+class MatrixMemoryMixer:
+    """Linear attention with exponential gating: q = W_q h dk^-1/2, k, v plain; log input gate i = cap tanh((W_i h + i.b) / cap), log forget gate
+    f = logsigmoid(cap tanh((W_f h + f.b) / cap)); with the running maximum m (0 at the start): m' = max(f + m, i), S <- e^(f + m - m') S + e^(i - m') k v^T,
+    n alike with k, o = S^T q / (max(|n . q|, e^(-m')) + 1e-6); each head's o over its root mean square, times norm [H dv], times sigmoid(g h), then o [D, H dv]."""
+    kind = "state"
+
+    def __init__(self, w: Dict[str, torch.Tensor], heads: int, dk: int, dv: int, cap: float, eps: float, dtype: torch.dtype):
+        self.H, self.dk, self.dv, self.cap, self.eps, self.dtype = heads, dk, dv, float(cap), eps, dtype
+        self.w_in = torch.cat([w["q"], w["k"], w["v"], w["g"], w["i"], w["f"]], 0).to(dtype).contiguous()
+        self.off_g = 2 * heads * dk + heads * dv
+        self.off_i = self.off_g + heads * dv
+        self.off_f = self.off_i + heads
+        self.i_bias = w["i.b"].float().contiguous() if "i.b" in w else None
+        self.f_bias = w["f.b"].float().contiguous() if "f.b" in w else None
+        self.norm = w["norm"].float().contiguous()
+        self.w_o = w["o"].to(dtype).contiguous()
+
+    def state_shapes(self):
+        nvb = -(-self.dv // 16)                     # the normaliser and the maximum are kept once per block of 16 value columns
+        return ((self.H, self.dv, self.dk), (self.H, nvb, self.dk), (self.H, nvb))
+
+    def forward(self, h: torch.Tensor, batch: StepBatch, cache, proj: Optional[torch.Tensor] = None) -> torch.Tensor:
+        S, n, m = cache
+        if proj is None:
+            proj = ops.linear(h, self.w_in)
+        gates = dict(off_i=self.off_i, off_f=self.off_f, i_bias=self.i_bias, f_bias=self.f_bias, cap=self.cap, normaliser=n, maximum=m)
+        o = ops.linear_attention(proj, 0, self.H * self.dk, 2 * self.H * self.dk, S, batch, self.H, self.dk, self.dv, q_scale=self.dk ** -0.5, gates=gates)
+        z = ops.group_rms_norm_gate(o, self.norm, proj[:, self.off_g:], self.H, self.eps, self.dtype)
+        return ops.linear(z, self.w_o)
+
+
+class ParallelMixer:
+    """Two mixers on the same input, one fused input projection; result = (rms(left) * left_out + rms(right) * right_out) / 2 over the model width.
+    ``left`` keeps a paged cache, ``right`` a state."""
+    kind = "both"
+
+    def __init__(self, left, right, left_out: torch.Tensor, right_out: torch.Tensor, eps: float):
+        self.left, self.right, self.eps = left, right, eps
+        self.w_in = torch.cat([left.w_in, right.w_in], 0).contiguous()
+        self.split = left.w_in.shape[0]
+        self.left_out, self.right_out = (0.5 * left_out.float()).contiguous(), (0.5 * right_out.float()).contiguous()       # the halving is exact in the weights
+
+    def cache_shape(self):
+        return self.left.cache_shape()
+
+    def state_shapes(self):
+        return self.right.state_shapes()
+
+    def forward(self, h: torch.Tensor, batch: StepBatch, kv, state) -> torch.Tensor:
+        proj = ops.linear(h, self.w_in)
+        a = self.left.forward(h, batch, kv, proj=proj[:, :self.split])
+        b = self.right.forward(h, batch, state, proj=proj[:, self.split:])
+        y = ops.rms_norm_ex(a, self.left_out, self.eps, 0.0, torch.float32)
+        return ops.rms_norm_ex(b, self.right_out, self.eps, 0.0, torch.float32, residual=y, out=y)

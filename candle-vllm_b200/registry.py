@@ -26,7 +26,7 @@ def architecture_of(config: dict) -> str:
 
 
 # the source group (build.GROUPS) whose library alone serves an architecture, for a first start from a source-only checkout
-_BUILD_GROUP = {"Gobesun": "ragged", "Guvusun": "latent"}
+_BUILD_GROUP = {"Gobesun": "ragged", "Guvusun": "latent", "Panarax": "hybrid"}
 
 
 def build_group_of(path: str) -> str:
@@ -56,6 +56,11 @@ def _guvusun(path, **kw):
     return GuvusunModel.from_pretrained(path, **kw)
 
 
+def _panarax(path, **kw):
+    from .panarax import PanaraxModel
+    return PanaraxModel.from_pretrained(path, **kw)
+
+
 def _llama(path, **kw):
     from .llama import load_dense_checkpoint
     return load_dense_checkpoint(path, **kw)
@@ -63,4 +68,5 @@ def _llama(path, **kw):
 
 register_model("Gobesun", _gobesun)
 register_model("Guvusun", _guvusun)
+register_model("Panarax", _panarax)
 register_model("LlamaForCausalLM", _llama)

@@ -171,15 +171,20 @@ def gated_rms_norm(o: torch.Tensor, gate: torch.Tensor, weight: torch.Tensor, he
 
 def qk_norm_rope_cache(qkv: torch.Tensor, q_norm: Optional[torch.Tensor], k_norm: Optional[torch.Tensor], cos: Optional[torch.Tensor],
                        sin: Optional[torch.Tensor], batch: StepBatch, k_cache: torch.Tensor, v_cache: torch.Tensor, heads: int, kv_heads: int, dk: int,
-                       dv: int, rot_dims: int, eps: float, q_dtype: torch.dtype = torch.float32) -> torch.Tensor:
+                       dv: int, rot_dims: int, eps: float, q_dtype: torch.dtype = torch.float32, q_temp: Optional[tuple] = None,
+                       v_unit_rms: bool = False) -> torch.Tensor:
+    """``q_temp`` = (coef, every): the query at position p is multiplied by 1 + coef ln(floor((p + 1) / every) + 1); ``v_unit_rms``: every value head is
+    cached divided by its root mean square."""
     T = qkv.shape[0]
     if cos is not None and batch.max_position >= cos.shape[0]:
         raise BackendError(f"position {batch.max_position} is outside the rotary table ({cos.shape[0]} rows)")
     q = torch.empty((T, heads * dk), dtype=q_dtype, device=qkv.device)
-    lib().qk_norm_rope_cache(_ptr(qkv), C.c_int64(qkv.stride(0) if T > 1 else qkv.shape[1]), _ptr(q_norm), _ptr(k_norm), _ptr(cos), _ptr(sin),
-                             C.c_int32(0 if cos is None else cos.shape[0]), _ptr(batch.positions), _ptr(batch.slot_mapping), _ptr(q), _ptr(k_cache),
-                             _ptr(v_cache), C.c_int32(T), C.c_int32(heads), C.c_int32(kv_heads), C.c_int32(dk), C.c_int32(dv), C.c_int32(rot_dims),
-                             C.c_float(eps), C.c_int32(_tag(k_cache.dtype)), C.c_int32(_tag(q_dtype)), _stream(qkv.device))
+    coef, every = q_temp if q_temp else (0.0, 0)
+    lib().qk_norm_rope_cache_ex(_ptr(qkv), C.c_int64(qkv.stride(0) if T > 1 else qkv.shape[1]), _ptr(q_norm), _ptr(k_norm), _ptr(cos), _ptr(sin),
+                                C.c_int32(0 if cos is None else cos.shape[0]), _ptr(batch.positions), _ptr(batch.slot_mapping), _ptr(q), _ptr(k_cache),
+                                _ptr(v_cache), C.c_int32(T), C.c_int32(heads), C.c_int32(kv_heads), C.c_int32(dk), C.c_int32(dv), C.c_int32(rot_dims),
+                                C.c_float(eps), C.c_float(coef), C.c_int32(every), C.c_int32(1 if v_unit_rms else 0), C.c_int32(_tag(k_cache.dtype)),
+                                C.c_int32(_tag(q_dtype)), _stream(qkv.device))
     check("qk_norm_rope_cache")
     return q
 
@@ -353,28 +358,32 @@ def linear_grouped(x: torch.Tensor, weight: torch.Tensor, tile_group: torch.Tens
     return out
 
 
-def moe_route(logits: torch.Tensor, correction: Optional[torch.Tensor], top: int, groups: int, keep: int, scale: float):
-    """f32 [T, N] -> (ids i32 [T, top], weights f32 [T, top])"""
+def moe_route(logits: torch.Tensor, correction: Optional[torch.Tensor], top: int, groups: int, keep: int, scale: float, score: str = "softmax",
+              normalise: bool = True):
+    """f32 [T, N] -> (ids i32 [T, top], weights f32 [T, top]); ``score`` softmax over the outputs or a sigmoid per output; ``normalise`` False leaves the
+    chosen scores (times scale) as they are"""
     T, N = logits.shape
     ids = torch.empty((T, top), dtype=torch.int32, device=logits.device)
     w = torch.empty((T, top), dtype=torch.float32, device=logits.device)
-    lib().moe_route(_ptr(logits), C.c_int64(logits.stride(0) if T > 1 else max(N, logits.stride(0))), _ptr(correction), _ptr(ids), _ptr(w), C.c_int32(T), C.c_int32(N),
-                    C.c_int32(top), C.c_int32(groups), C.c_int32(keep), C.c_float(scale), _stream(logits.device))
+    lib().moe_route_ex(_ptr(logits), C.c_int64(logits.stride(0) if T > 1 else max(N, logits.stride(0))), _ptr(correction), _ptr(ids), _ptr(w), C.c_int32(T), C.c_int32(N),
+                       C.c_int32(top), C.c_int32(groups), C.c_int32(keep), C.c_float(scale), C.c_int32({"softmax": 0, "sigmoid": 1}[score]), C.c_int32(1 if normalise else 0),
+                       _stream(logits.device))
     check("moe_route")
     return ids, w
 
 
-def moe_gate_up(h: torch.Tensor, w_gate_up: torch.Tensor, ids: torch.Tensor, order: Optional[torch.Tensor] = None) -> torch.Tensor:
+def moe_gate_up(h: torch.Tensor, w_gate_up: torch.Tensor, ids: torch.Tensor, order: Optional[torch.Tensor] = None, act: str = "silu", limit: float = 0.0,
+                pair_scale: Optional[torch.Tensor] = None) -> torch.Tensor:
     """h [T, D], w_gate_up [E, 2 ff, D] of one dtype -> act [T * top, ff] (rows of identity choices are left unwritten); ``order`` i32 [T * top]: the
     pairs in the order the blocks take them (sorted by expert, so that neighbours share weights)"""
     T, D = h.shape
     E, ff2, _ = w_gate_up.shape
     top = ids.shape[1]
-    act = torch.empty((T * top, ff2 // 2), dtype=h.dtype, device=h.device)
-    lib().moe_gate_up(_ptr(h), C.c_int64(h.stride(0) if T > 1 else max(D, h.stride(0))), _ptr(w_gate_up), _ptr(ids), _ptr(order), _ptr(act), C.c_int32(T), C.c_int32(top), C.c_int32(E),
-                      C.c_int32(ff2 // 2), C.c_int32(D), C.c_int32(_tag(h.dtype)), _stream(h.device))
+    out = torch.empty((T * top, ff2 // 2), dtype=h.dtype, device=h.device)
+    lib().moe_gate_up_ex(_ptr(h), C.c_int64(h.stride(0) if T > 1 else max(D, h.stride(0))), _ptr(w_gate_up), _ptr(ids), _ptr(order), _ptr(out), C.c_int32(T), C.c_int32(top),
+                         C.c_int32(E), C.c_int32(ff2 // 2), C.c_int32(D), C.c_int32(GLU_ACTS[act]), C.c_float(limit), _ptr(pair_scale), C.c_int32(_tag(h.dtype)), _stream(h.device))
     check("moe_gate_up")
-    return act
+    return out
 
 
 def moe_down(act: torch.Tensor, w_down: torch.Tensor, ids: torch.Tensor, order: torch.Tensor) -> torch.Tensor:
@@ -418,9 +427,10 @@ def silu_mul_packed(gate_up: torch.Tensor, out_dtype: torch.dtype) -> torch.Tens
     return out
 
 
-def moe_combine_rows(y: torch.Tensor, pair_row: torch.Tensor, weights: torch.Tensor, x: torch.Tensor) -> torch.Tensor:
+def moe_combine_rows(y: torch.Tensor, pair_row: torch.Tensor, weights: Optional[torch.Tensor], x: torch.Tensor) -> torch.Tensor:
+    """weights None: every choice counts once (the weight was applied elsewhere)"""
     T, D = x.shape
-    top = weights.shape[1]
+    top = pair_row.numel() // T
     out = torch.empty((T, D), dtype=torch.float32, device=x.device)
     lib().moe_combine_rows(_ptr(y), _ptr(pair_row), _ptr(weights), _ptr(x), C.c_int64(x.stride(0) if T > 1 else max(D, x.stride(0))), _ptr(out), C.c_int32(T),
                            C.c_int32(top), C.c_int32(D), _stream(x.device))
@@ -477,4 +487,142 @@ def latent_attention_decode(q_abs: torch.Tensor, q_rot: torch.Tensor, c_cache: t
                                    _ptr(sink), C.c_int32(n), C.c_int32(n), C.c_int32(H), C.c_int32(R), C.c_int32(q_rot.shape[2]), C.c_int32(bs), C.c_int32(W),
                                    C.c_int64(c_cache.shape[0]), C.c_float(scale), C.c_int32(DType.BF16), _ptr(ws), C.c_size_t(need), _stream(q_abs.device))
         check("latent_attention_decode")
+    return out
+
+
+# ---- position embeddings, layer norm, gated residuals, state-space and linear-attention mixers ----------------------------------------------
+
+def embedding_positional(table: torch.Tensor, pos_table: torch.Tensor, batch: StepBatch, scale: float = 1.0) -> torch.Tensor:
+    """table[token] * scale + pos_table[position] -> f32 [T, dim]; both tables of one dtype"""
+    vocab, dim = table.shape
+    if pos_table.dtype != table.dtype or pos_table.shape[1] != dim or not pos_table.is_contiguous():
+        raise BackendError(f"embedding_positional: position table {tuple(pos_table.shape)} {pos_table.dtype} beside {tuple(table.shape)} {table.dtype}")
+    if batch.max_position >= pos_table.shape[0]:
+        raise BackendError(f"position {batch.max_position} is outside the position table ({pos_table.shape[0]} rows)")
+    T = batch.tokens.shape[0]
+    out = torch.empty((T, dim), dtype=torch.float32, device=table.device)
+    lib().embedding_positional(_ptr(table), _ptr(pos_table), _ptr(batch.tokens), _ptr(batch.positions), _ptr(out), C.c_int32(T), C.c_int32(dim), C.c_int32(vocab),
+                               C.c_int32(pos_table.shape[0]), C.c_float(scale), C.c_int32(_tag(table.dtype)), _stream(table.device))
+    check("embedding_positional")
+    return out
+
+
+def layer_norm(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor], eps: float, out_dtype: torch.dtype, row_index: Optional[torch.Tensor] = None,
+               also_f32: bool = False):
+    """Layer norm of f32 rows with weight and bias -> rows of ``out_dtype``; ``also_f32`` returns (out, f32 copy) -- the same tensor twice when
+    out_dtype is f32.  ``row_index`` (i32) selects the rows."""
+    n = x.shape[-1]
+    rows = x.shape[0] if row_index is None else row_index.shape[0]
+    if x.dtype != torch.float32 or weight.dtype != torch.float32 or x.stride(-1) != 1:
+        raise BackendError("layer_norm: x and weight are f32")
+    out = torch.empty((rows, n), dtype=out_dtype, device=x.device)
+    out32 = torch.empty((rows, n), dtype=torch.float32, device=x.device) if also_f32 and out_dtype != torch.float32 else None
+    lib().layer_norm_ex(_ptr(x), _ptr(weight), _ptr(bias), _ptr(out), _ptr(out32), _ptr(row_index), C.c_int32(rows), C.c_int32(n),
+                        C.c_int64(x.stride(0) if x.shape[0] > 1 else n), C.c_float(eps), C.c_int32(_tag(out_dtype)), _stream(x.device))
+    check("layer_norm_ex")
+    if also_f32:
+        return out, (out if out32 is None else out32)
+    return out
+
+
+def gated_residual_add(x: torch.Tensor, y: torch.Tensor, gate_logits: Optional[torch.Tensor], gate_bias: Optional[torch.Tensor]) -> torch.Tensor:
+    """x += sigmoid(gate_logits + gate_bias) * y in place on the f32 stream x [T, n] (gate_logits None: x += y)"""
+    T, n = x.shape
+    if x.dtype != torch.float32 or not x.is_contiguous() or y.dtype != torch.float32 or y.stride(1) != 1 or (gate_logits is not None and gate_logits.stride(1) != 1):
+        raise BackendError("gated_residual_add: f32 tensors, x contiguous")
+    pitch = lambda t: t.stride(0) if T > 1 else max(n, t.stride(0))
+    lib().gated_residual_add(_ptr(x), _ptr(y), C.c_int64(pitch(y)), _ptr(gate_logits), C.c_int64(0 if gate_logits is None else pitch(gate_logits)), _ptr(gate_bias),
+                             C.c_int32(T), C.c_int32(n), _stream(x.device))
+    check("gated_residual_add")
+    return x
+
+
+GLU_ACTS = {"silu": 0, "gelu_tanh": 1, "clamped": 2}
+
+
+def glu_packed(gate_up: torch.Tensor, act: str, out_dtype: torch.dtype, limit: float = 0.0, row_scale: Optional[torch.Tensor] = None,
+               scale_index: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """act(gate) * up from f32 [rows, ff | ff]; ``row_scale`` (f32) first multiplies both halves of row r by row_scale[scale_index[r]] (or [r])"""
+    rows, two_ff = gate_up.shape
+    out = torch.empty((rows, two_ff // 2), dtype=out_dtype, device=gate_up.device)
+    lib().glu_packed(_ptr(gate_up), _ptr(out), C.c_int64(rows), C.c_int32(two_ff // 2), C.c_int64(gate_up.stride(0) if rows > 1 else two_ff), C.c_int32(GLU_ACTS[act]),
+                     C.c_float(limit), _ptr(row_scale), _ptr(scale_index), C.c_int32(_tag(out_dtype)), _stream(gate_up.device))
+    check("glu_packed")
+    return out
+
+
+def group_rms_norm_gate(o: torch.Tensor, weight: Optional[torch.Tensor], gate: Optional[torch.Tensor], groups: int, eps: float, out_dtype: torch.dtype,
+                        gate_act: str = "sigmoid") -> torch.Tensor:
+    """o f32 [T, n] -> o / rms(o over each of ``groups`` equal runs) * weight * act(gate)"""
+    T, n = o.shape
+    out = torch.empty((T, n), dtype=out_dtype, device=o.device)
+    pitch = lambda t: t.stride(0) if T > 1 else max(n, t.stride(0))
+    lib().group_rms_norm_gate(_ptr(o), C.c_int64(pitch(o)), _ptr(weight), _ptr(gate), C.c_int64(0 if gate is None else pitch(gate)), _ptr(out), C.c_int32(T), C.c_int32(n),
+                              C.c_int32(groups), C.c_float(eps), C.c_int32({"sigmoid": 0, "silu": 1}[gate_act]), C.c_int32(_tag(out_dtype)), _stream(o.device))
+    check("group_rms_norm_gate")
+    return out
+
+
+def causal_conv(x: torch.Tensor, taps: torch.Tensor, conv_state: torch.Tensor, batch: StepBatch, out_dtype: torch.dtype = torch.float32,
+                in_bias: Optional[torch.Tensor] = None, out_bias: Optional[torch.Tensor] = None, act: str = "none", add_input: bool = False) -> torch.Tensor:
+    """Causal convolution over time on each channel of x (f32 view [T, C], row stride allowed): act(taps * inputs + out_bias) (+ the input itself), the
+    inputs being x + in_bias; conv_state f32 [slots, max(K - 1, 1), C] is advanced in place."""
+    T, Cn = x.shape
+    K = taps.shape[1]
+    if T > 65535:
+        raise BackendError("causal_conv: at most 65535 rows per step")
+    if x.dtype != torch.float32 or taps.dtype != torch.float32 or taps.shape[0] != Cn or conv_state.shape[1:] != (max(K - 1, 1), Cn):
+        raise BackendError(f"causal_conv: x {tuple(x.shape)}, taps {tuple(taps.shape)}, state {tuple(conv_state.shape)}")
+    y = torch.empty((T, Cn), dtype=out_dtype, device=x.device)
+    lib().causal_conv_ex(_ptr(x), C.c_int64(x.stride(0) if T > 1 else max(Cn, x.stride(0))), _ptr(in_bias), _ptr(taps), _ptr(out_bias), _ptr(conv_state), _ptr(y),
+                         C.c_int64(Cn), _ptr(batch.token_seq), _ptr(batch.cu_seqlens), _ptr(batch.seq_slots), _ptr(batch.seq_start), C.c_int32(T),
+                         C.c_int32(batch.num_seqs), C.c_int32(Cn), C.c_int32(K), C.c_int32({"none": 0, "silu": 1}[act]), C.c_int32(1 if add_input else 0),
+                         C.c_int32(_tag(out_dtype)), _stream(x.device))
+    check("causal_conv_ex")
+    return y
+
+
+def block_diag_linear(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor]) -> torch.Tensor:
+    """x f32 [T, blocks * N] (row stride allowed), weight f32 [blocks, M, N] -> f32 [T, blocks * M]: every block of N neighbouring channels times its own matrix"""
+    T = x.shape[0]
+    nb, M, N = weight.shape
+    if x.dtype != torch.float32 or weight.dtype != torch.float32 or not weight.is_contiguous() or x.shape[1] != nb * N or x.stride(1) != 1:
+        raise BackendError(f"block_diag_linear: x {tuple(x.shape)} {x.dtype}, weight {tuple(weight.shape)} {weight.dtype}")
+    out = torch.empty((T, nb * M), dtype=torch.float32, device=x.device)
+    lib().block_diag_linear(_ptr(x), C.c_int64(x.stride(0) if T > 1 else max(nb * N, x.stride(0))), _ptr(weight), _ptr(bias), _ptr(out), C.c_int64(nb * M), C.c_int32(T),
+                            C.c_int32(nb), C.c_int32(M), C.c_int32(N), _stream(x.device))
+    check("block_diag_linear")
+    return out
+
+
+def gated_linear_scan(u: torch.Tensor, gates: torch.Tensor, lam: torch.Tensor, y_pre: torch.Tensor, y_bias: Optional[torch.Tensor], state: torch.Tensor, batch: StepBatch,
+                      block_channels: int, decay_scale: float, out_dtype: torch.dtype) -> torch.Tensor:
+    """u f32 [T, C]; gates f32 [T, blocks, 2 n] (recurrence gate, then input gate, per block); y_pre f32 view [T, C]; state f32 [slots, C] advanced in place
+    -> S_t * gelu_tanh(y_pre + y_bias) of ``out_dtype``"""
+    T, Cn = u.shape
+    out = torch.empty((T, Cn), dtype=out_dtype, device=u.device)
+    pitch = lambda t, n: t.stride(0) if T > 1 else max(n, t.stride(0))
+    lib().gated_linear_scan(_ptr(u), C.c_int64(pitch(u, Cn)), _ptr(gates), C.c_int64(pitch(gates, 2 * Cn)), _ptr(lam), _ptr(y_pre), C.c_int64(pitch(y_pre, Cn)), _ptr(y_bias),
+                            _ptr(state), _ptr(out), _ptr(batch.cu_seqlens), _ptr(batch.seq_slots), _ptr(batch.seq_start), C.c_int32(batch.num_seqs), C.c_int32(Cn),
+                            C.c_int32(block_channels), C.c_float(decay_scale), C.c_int32(_tag(out_dtype)), _stream(u.device))
+    check("gated_linear_scan")
+    return out
+
+
+def linear_attention(proj: torch.Tensor, off_q: int, off_k: int, off_v: int, state: torch.Tensor, batch: StepBatch, heads: int, dk: int, dv: int, act: str = "none",
+                     q_scale: float = 1.0, decay: Optional[torch.Tensor] = None, gates: Optional[dict] = None) -> torch.Tensor:
+    """S <- a S + b k v^T, o = S^T q per head on columns of ``proj`` (f32 [T, ld]); state f32 [slots, H, dv, dk] advanced in place.  ``decay`` f32 [H]: a fixed
+    decay per head.  ``gates`` = dict(off_i, off_f, i_bias, f_bias, cap, normaliser, maximum): exponential gating with a running maximum and a normaliser
+    (states [slots, H, ceil(dv / 16), dk] and [slots, H, ceil(dv / 16)]).  -> f32 [T, H dv]"""
+    T = proj.shape[0]
+    out = torch.empty((T, heads * dv), dtype=torch.float32, device=proj.device)
+    if (decay is None) == (gates is None):
+        raise BackendError("linear_attention: either a fixed decay or exponential gates")
+    g = gates or {}
+    lib().linear_attention(_ptr(proj), C.c_int64(proj.stride(0) if T > 1 else proj.shape[1]), C.c_int32(off_q), C.c_int32(off_k), C.c_int32(off_v),
+                           C.c_int32(g.get("off_i", 0)), C.c_int32(g.get("off_f", 0)), _ptr(decay), _ptr(g.get("i_bias")), _ptr(g.get("f_bias")),
+                           C.c_float(g.get("cap", 0.0)), C.c_float(q_scale), C.c_int32({"none": 0, "silu": 1}[act]), C.c_int32(0 if gates is None else 1), _ptr(state),
+                           _ptr(g.get("normaliser")), _ptr(g.get("maximum")), _ptr(out), _ptr(batch.cu_seqlens), _ptr(batch.seq_slots), _ptr(batch.seq_start),
+                           C.c_int32(batch.num_seqs), C.c_int32(heads), C.c_int32(dk), C.c_int32(dv), _stream(proj.device))
+    check("linear_attention")
     return out

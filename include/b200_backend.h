@@ -561,6 +561,68 @@ void moe_gate_up(const void* h, int64_t ldh, const void* w_gate_up, const int32_
 void moe_down(const void* act, const void* w_down, const int32_t* ids, const int32_t* order, float* y, int32_t rows, int32_t num_experts, int32_t ff, int32_t width,
               int32_t dtype, int64_t stream);
 
+/* ---- position embeddings, layer norm, gated residuals, state-space and linear-attention mixers for ragged steps (csrc/norm_act.cu,
+ *      linear_recurrence.cu, attention_varlen.cu, moe_ragged.cu) ------------------------------------------------------------------------------------
+ * embedding_positional: out f32 [T, dim] = table[ids[t]] * scale + pos_table[positions[t]]; both tables of table_dtype (F32 / BF16), pos_table
+ *   [max_pos, dim].
+ * layer_norm_ex: (x[src] - mean) / sqrt(var + eps) * weight + bias (bias may be null), biased variance, src = row_index ? row_index[r] : r; written
+ *   to out (out_dtype F32 / BF16; may be null) and / or out32 (f32; may be null).
+ * gated_residual_add: x[r, c] += sigmoid(gate_logits[r, c] + gate_bias[c]) * y[r, c] in place on the f32 stream; gate_logits null: x += y.
+ * glu_packed: out[r, :ff] = act(g) * u from f32 gate_up [rows, ff | ff] (row pitch ld); act 0 = SiLU, 1 = tanh GELU, 2 = clamped: g' = min(g, limit),
+ *   u' = clamp(u, -limit, limit), out = g' sigmoid(1.702 g') (u' + 1).  row_scale (f32, may be null) multiplies g and u first: row r takes
+ *   row_scale[scale_index ? scale_index[r] : r]; a negative index marks a padding row, written as zeros.
+ * group_rms_norm_gate: out[t, c] = o[t, c] / rms(o[t, group of c]) * weight[c] * act(gate[t, c]); n columns in `groups` equal runs; weight / gate may
+ *   be null; gate_act 0 = sigmoid, 1 = SiLU.
+ * causal_conv_ex: y[t, c] = act(sum_j taps[c, j] in[t - K + 1 + j, c] + out_bias[c]) (+ in[t, c] when add_input), in = x + in_bias (zeros before a
+ *   sequence's start); conv_state f32 [slots, max(K - 1, 1), channels] holds a sequence's last K - 1 inputs and is rolled forward.  act 0 = none,
+ *   1 = SiLU; y of out_dtype F32 / BF16 with row pitch ldy.
+ * block_diag_linear: out[t, b M + j] = sum_i weight[b, j, i] x[t, b N + i] + bias[b M + j], M = rows_per_block, N = cols_per_block; all f32, true
+ *   32-bit products.
+ * gated_linear_scan: per channel c of block c / block_channels: r = sigmoid(gates[t, blk, j]), i = sigmoid(gates[t, blk, n + j]) (gates f32 [T, blocks,
+ *   2 n], n = block_channels, j = c mod n); log a = -decay_scale r softplus(lam[c]); S <- a S + sqrt(1 - a^2) i u[t, c]; out[t, c] = S *
+ *   gelu_tanh(y_pre[t, c] + y_bias[c]).  state f32 [slots, channels].
+ * linear_attention: per head, S f32 [dk, dv] (stored [slots, H, dv, dk]): S <- a S + b k v^T, o = S^T q; q, k, v = columns off_q / off_k / off_v of
+ *   proj f32 [T, ld] (head-major), through SiLU when act == 1, q also times q_scale.  gating 0: a = decay[h], b = 1.  gating 1: with i = cap
+ *   tanh((proj[off_i + h] + i_bias[h]) / cap), f = logsigmoid(cap tanh((proj[off_f + h] + f_bias[h]) / cap)) and the running maximum m (0 at the
+ *   start) m' = max(f + m, i): a = e^(f + m - m'), b = e^(i - m'), normaliser n <- a n + b k, o = S^T q / (max(|n . q|, e^(-m')) + 1e-6);
+ *   normaliser f32 [slots, H, ceil(dv / 16), dk] and maximum f32 [slots, H, ceil(dv / 16)] (one copy per block of 16 value columns).  out f32
+ *   [T, H dv].  dk <= 256.
+ * qk_norm_rope_cache_ex: qk_norm_rope_cache plus a query temperature (q times 1 + q_temp_coef ln(floor((p + 1) / q_temp_every) + 1); every 0 = off)
+ *   and, with v_unit_rms, values divided by their root mean square per head (eps inside the root) before they are cached.
+ * moe_route_ex: moe_route with score_fn 0 = softmax, 1 = sigmoid per output, and normalise 0 = the chosen scores times scale as they are.
+ * moe_gate_up_ex: moe_gate_up with act_fn 0 = SiLU, 2 = the clamped form of glu_packed, and pair_scale (f32 [T top], may be null) multiplying both
+ *   products of a pair before the activation. */
+void embedding_positional(const void* table, const void* pos_table, const int32_t* ids, const int32_t* positions, float* out, int32_t num_tokens, int32_t dim,
+                          int32_t vocab, int32_t max_pos, float scale, int32_t table_dtype, int64_t stream);
+void layer_norm_ex(const float* x, const float* weight, const float* bias, void* out, float* out32, const int32_t* row_index, int32_t rows, int32_t n, int64_t ldx,
+                   float eps, int32_t out_dtype, int64_t stream);
+void gated_residual_add(float* x, const float* y, int64_t ldy, const float* gate_logits, int64_t ld_gate, const float* gate_bias, int32_t rows, int32_t n,
+                        int64_t stream);
+void glu_packed(const float* gate_up, void* out, int64_t rows, int32_t ff, int64_t ld, int32_t act, float limit, const float* row_scale, const int32_t* scale_index,
+                int32_t out_dtype, int64_t stream);
+void group_rms_norm_gate(const float* o, int64_t ldo, const float* weight, const float* gate, int64_t ld_gate, void* out, int32_t num_tokens, int32_t n,
+                         int32_t groups, float eps, int32_t gate_act, int32_t out_dtype, int64_t stream);
+void causal_conv_ex(const float* x, int64_t ldx, const float* in_bias, const float* taps, const float* out_bias, float* conv_state, void* y, int64_t ldy,
+                    const int32_t* token_seq, const int32_t* cu_seqlens, const int32_t* seq_slots, const int32_t* seq_start, int32_t num_tokens,
+                    int32_t num_seqs, int32_t channels, int32_t num_taps, int32_t act, int32_t add_input, int32_t out_dtype, int64_t stream);
+void block_diag_linear(const float* x, int64_t ldx, const float* weight, const float* bias, float* out, int64_t ldy, int32_t num_tokens, int32_t blocks,
+                       int32_t rows_per_block, int32_t cols_per_block, int64_t stream);
+void gated_linear_scan(const float* u, int64_t ldu, const float* gates, int64_t ld_gates, const float* lam, const float* y_pre, int64_t ldy, const float* y_bias,
+                       float* state, void* out, const int32_t* cu_seqlens, const int32_t* seq_slots, const int32_t* seq_start, int32_t num_seqs, int32_t channels,
+                       int32_t block_channels, float decay_scale, int32_t out_dtype, int64_t stream);
+void linear_attention(const float* proj, int64_t ld, int32_t off_q, int32_t off_k, int32_t off_v, int32_t off_i, int32_t off_f, const float* decay,
+                      const float* i_bias, const float* f_bias, float gate_cap, float q_scale, int32_t act, int32_t gating, float* state, float* normaliser,
+                      float* maximum, float* out, const int32_t* cu_seqlens, const int32_t* seq_slots, const int32_t* seq_start, int32_t num_seqs,
+                      int32_t num_heads, int32_t dk, int32_t dv, int64_t stream);
+void qk_norm_rope_cache_ex(const float* qkv, int64_t ld, const float* q_norm_w, const float* k_norm_w, const float* cos_t, const float* sin_t,
+                           int32_t max_pos, const int32_t* positions, const int64_t* slot_mapping, void* q_out, void* key_cache, void* value_cache,
+                           int32_t num_tokens, int32_t num_heads, int32_t num_kv_heads, int32_t dk, int32_t dv, int32_t rot_dims, float eps,
+                           float q_temp_coef, int32_t q_temp_every, int32_t v_unit_rms, int32_t cache_dtype, int32_t q_dtype, int64_t stream);
+void moe_route_ex(const float* logits, int64_t ld, const float* correction, int32_t* ids, float* weights, int32_t num_tokens, int32_t num_outputs, int32_t top,
+                  int32_t groups, int32_t keep, float scale, int32_t score_fn, int32_t normalise, int64_t stream);
+void moe_gate_up_ex(const void* h, int64_t ldh, const void* w_gate_up, const int32_t* ids, const int32_t* order, void* act, int32_t num_tokens, int32_t top,
+                    int32_t num_experts, int32_t ff, int32_t width, int32_t act_fn, float limit, const float* pair_scale, int32_t dtype, int64_t stream);
+
 #ifdef __cplusplus
 }
 #endif
