@@ -49,10 +49,10 @@ def parse():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--cpu-seconds", type=float, default=20.0)
     ap.add_argument("--parity-steps", type=int, default=3, help="decode steps compared against a TP=1 engine before timing (0 = off)")
-    ap.add_argument("--arch", default="llama", choices=["llama", "gobesun", "guvusun"],
+    ap.add_argument("--arch", default="llama", choices=["llama", "gobesun", "guvusun", "panarax"],
                     help="llama = the metric (default, unchanged).  gobesun = prefill / decode throughput of the Gobesun decoder at layer sizes of real "
                          "models (random weights), beside a dense bf16 Llama of equal width / heads / ff / depth, with a per-kernel roofline table; "
-                         "one JSON line, single GPU.")
+                         "one JSON line, single GPU.  guvusun / panarax = the same for those decoders (panarax beside a Gobesun of equal width / heads / ff / depth).")
     ap.add_argument("--arch-sizes", default="w2048,w4096")
     return ap.parse_args()
 
@@ -1061,10 +1061,213 @@ def run_guvusun(args):
                       "gpu_launches": int(pkg.lib().b200_total_kernel_launches() - l0), "sizes": results}))
 
 
+# ------------------------------------------------------------------------------------------------
+# --arch panarax: recurrence / linear attention / softmax attention + matrix memory, dense and routed feed-forwards, beside a Gobesun of equal size
+# ------------------------------------------------------------------------------------------------
+PANARAX_SIZES = {
+    "w2048": dict(width=2048, heads=16, kv=4, ff=5632, vocab=32000, layers=8, experts=8, top=2),
+    "w4096": dict(width=4096, heads=32, kv=8, ff=11008, vocab=32000, layers=4, experts=8, top=2),
+}
+
+
+def run_panarax(args):
+    import torch
+    import candle_vllm_b200 as pkg
+    from candle_vllm_b200 import seq_ops as ops, synthetic as S
+    from candle_vllm_b200.engine import ModelRunner
+    from candle_vllm_b200.gobesun import GobesunConfig, GobesunModel
+    from candle_vllm_b200.panarax import PanaraxConfig, PanaraxModel
+
+    torch.cuda.set_device(0)
+    dev = "cuda"
+    peaks = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json"))) if os.path.exists(os.path.join(ROOT, "MEASURED_PEAKS.json")) else \
+        {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "fallback": True}
+    HBM, TC = peaks["hbm_gbs"] * 1e9, peaks["bf16_tflops"] * 1e12
+    props = torch.cuda.get_device_properties(0)
+    F32 = props.multi_processor_count * 128 * 2 * 1.965e9            # nominal f32 multiply-add rate: the recurrences are 32-bit by definition
+    K, W = max(args.steps, 1), max(args.warmup, 3)
+    P, B, CTX, hd = 4096, 32, 1024, 128
+    bf = torch.bfloat16
+    l0 = pkg.lib().b200_total_kernel_launches()
+
+    def timed(fn, reps, warm=3):
+        for _ in range(warm):
+            fn()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(reps):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) / reps * 1e-3
+
+    names = ["linear", "linear_grouped", "rms_norm_ex", "layer_norm", "gelu_tanh_mul", "glu_packed", "embedding_scaled", "embedding_positional", "causal_conv_silu",
+             "causal_conv", "gated_delta_rule", "gated_rms_norm", "group_rms_norm_gate", "block_diag_linear", "gated_linear_scan", "linear_attention", "qk_norm_rope_cache",
+             "paged_attention_varlen", "paged_attention_decode_chunked", "head_gate", "gated_residual_add", "moe_route", "moe_sorted_rows", "moe_gather_rows",
+             "moe_combine_rows", "moe_gate_up", "moe_down"]
+
+    def measure(model, V):
+        """(prefill s, decode s per step incl. host, decode s per step device, {(tag, kernel): [s]})"""
+        blocks_per = -(-(CTX + K + W + 8) // 64)
+        runner = ModelRunner(model, B * blocks_per + P // 64 + 1, B + 1, 64, decode_graphs=True, max_blocks_per_seq=blocks_per)
+        toks = torch.randint(0, V, (P,), generator=torch.Generator().manual_seed(1)).tolist()
+
+        def prefill():
+            runner.admit(10 ** 6)
+            runner.execute([dict(seq_id=10 ** 6, tokens=toks, want=[P - 1])])
+            runner.release(10 ** 6)
+        pre = timed(prefill, 3, 2)
+        for i in range(B):
+            runner.admit(i)
+        for i in range(0, B, 4):
+            runner.execute([dict(seq_id=j, tokens=toks[:CTX], want=[]) for j in range(i, i + 4)])
+        step_entries = lambda: [dict(seq_id=j, tokens=[toks[j]], want=[0]) for j in range(B)]
+        dec = timed(lambda: runner.execute(step_entries()), K, W)
+        dec_dev = timed(runner._graphs[B].graph.replay, K, 3)
+        kern = {}
+        orig = {n: getattr(ops, n) for n in names}
+
+        def instrument(tag):
+            def wrap(n):
+                def f(*a, **k):
+                    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                    torch.cuda.synchronize(); e0.record()
+                    r = orig[n](*a, **k)
+                    e1.record(); torch.cuda.synchronize()
+                    key = n
+                    if n == "linear":
+                        key = f"linear[{a[1].shape[0]}x{a[1].shape[1]}]"
+                    elif n == "linear_grouped":
+                        key = f"linear_grouped[{a[1].shape[0]}x{a[1].shape[1]}x{a[1].shape[2]}]"
+                    elif n == "linear_attention":
+                        key = "linear_attention[" + ("decay" if k.get("decay") is not None else "exp") + "]"
+                    kern.setdefault((tag, key), []).append(e0.elapsed_time(e1) * 1e-3)
+                    return r
+                return f
+            for n in names:
+                setattr(ops, n, wrap(n))
+        instrument("prefill")
+        prefill(); kern.clear(); prefill()
+        runner.decode_graphs = False
+        instrument("decode")
+        runner.execute(step_entries())
+        for k in [k for k in kern if k[0] == "decode"]:
+            kern.pop(k)
+        runner.execute(step_entries())
+        for n in names:
+            setattr(ops, n, orig[n])
+        del runner
+        torch.cuda.empty_cache()
+        return pre, dec, dec_dev, kern
+
+    sampler = ClockSampler(0); sampler.start()
+    results = {}
+    for name in [n for n in args.arch_sizes.split(",") if n in PANARAX_SIZES]:
+        z = PANARAX_SIZES[name]
+        D, H, G, ff, V, NL, E, top = z["width"], z["heads"], z["kv"], z["ff"], z["vocab"], z["layers"], z["experts"], z["top"]
+        # ---- Panarax: parallel, recurrence, lightning, lightning in turn; dense and routed feed-forwards alternate (the routed ones with top x expert ff = ff)
+        layers = []
+        for i in range(NL):
+            mlp = dict(ff=ff) if i % 2 == 0 else dict(ff=ff // top, experts=E, top=top)
+            if i % 4 == 0:
+                layers.append(S.panarax_parallel_layer(H, G, hd, hd, H // 2, hd, hd, q_temp=(0.1, 1024), **mlp))
+            elif i % 4 == 1:
+                layers.append(S.panarax_rglru_layer(D, H, conv=4, **mlp))
+            else:
+                layers.append(S.panarax_lightning_layer(H, hd, hd, **mlp))
+        cfg = S.panarax_config(D, V, layers, max_positions=P + 64, taps=3)
+        model = PanaraxModel(PanaraxConfig.from_dict(cfg), S.panarax_weights(cfg, 0), dtype=bf, block_size=64, device=dev)
+        p_pre, p_dec, p_dec_dev, p_kern = measure(model, V)
+        del model
+        torch.cuda.empty_cache()
+        # ---- Gobesun of equal width / heads / ff / depth: three recurrent layers to one attention layer
+        glayers = [S.gobesun_attention_layer(H, G, hd, hd, 2048, 64, ff=ff, base=1e6) if i % 4 == 3 else S.gobesun_delta_layer(H, H // 2, hd, hd, conv=4, ff=ff)
+                   for i in range(NL)]
+        gcfg = S.gobesun_config(D, V, glayers)
+        gmodel = GobesunModel(GobesunConfig.from_dict(gcfg), S.gobesun_weights(gcfg, 0), dtype=bf, block_size=64, max_pos=P + 64, device=dev)
+        g_pre, g_dec, g_dec_dev, g_kern = measure(gmodel, V)
+        del gmodel
+        torch.cuda.empty_cache()
+        med = lambda v: sorted(v)[len(v) // 2]
+        esz, Hm, Gd = 2, H // 2, H // 2
+        Cd = 2 * Gd * hd + H * hd
+        n_blk = D // H
+
+        def work(tag, key, T):
+            """algorithmic work of one call: ("bytes", n) against the measured copy bandwidth, ("flops", n) against the measured bf16 GEMM rate, ("f32", n)
+            against the nominal f32 multiply-add rate"""
+            pre = tag == "prefill"
+            if key.startswith("linear["):
+                n, k = (int(v) for v in key[7:-1].split("x"))
+                if n == V and pre:
+                    T = 1
+                return ("flops", 2.0 * T * n * k) if (pre and T > 1) else ("bytes", n * k * esz + T * (k * esz + n * 4))
+            if key.startswith("linear_grouped["):
+                g, n, k = (int(v) for v in key[15:-1].split("x"))
+                return ("flops", 2.0 * T * top * n * k) if pre else ("bytes", min(g, T * top) * n * k * esz + T * top * (k * esz + n * 4))
+            state = lambda per_seq: (1 if pre else T) * 2 * per_seq * 4            # one read and one write of every entry's state
+            table = {
+                "rms_norm_ex": ("bytes", T * D * (4 + esz)), "layer_norm": ("bytes", T * D * (4 + esz)),
+                "gelu_tanh_mul": ("bytes", T * ff * (8 + esz)), "glu_packed": ("bytes", T * ff * (8 + esz)),
+                "embedding_scaled": ("bytes", T * D * (esz + 4)), "embedding_positional": ("bytes", T * D * (2 * esz + 4)),
+                "causal_conv_silu": ("bytes", T * Cd * 8), "causal_conv": ("bytes", T * D * (4 + esz)),
+                "gated_rms_norm": ("bytes", T * H * hd * (8 + esz)), "group_rms_norm_gate": ("bytes", T * H * hd * (8 + esz)),
+                "gated_residual_add": ("bytes", T * D * 16), "head_gate": ("bytes", T * H * hd * 2 * esz),
+                "qk_norm_rope_cache": ("bytes", T * ((H + 2 * G) * hd * 4 + H * hd * esz + 2 * G * hd * esz)),
+                "gated_delta_rule": ("bytes", T * (Cd + H * hd) * 4) if not pre else ("f32", 6.0 * T * H * hd * hd),
+                "linear_attention[decay]": ("bytes", T * 4 * H * hd * 4 + state(H * hd * hd)) if not pre else ("f32", 4.0 * T * H * hd * hd),
+                "linear_attention[exp]": ("bytes", T * 4 * Hm * hd * 4 + state(Hm * hd * hd)) if not pre else ("f32", 4.0 * T * Hm * hd * hd),
+                "block_diag_linear": ("f32", 2.0 * T * D * 2 * n_blk) if pre else ("bytes", 2 * D * n_blk * 4 + T * D * 12),
+                "gated_linear_scan": ("bytes", T * D * (16 + esz) + state(D)),
+                "paged_attention_varlen": ("flops", 4.0 * H * hd * T * (T + 1) / 2) if pre else ("bytes", T * CTX * 2 * G * hd * esz),
+                "paged_attention_decode_chunked": ("bytes", T * CTX * 2 * G * hd * esz),
+            }
+            if key == "gated_delta_rule" and not pre:
+                return ("bytes", T * (Cd + H * hd) * 4 + state(H * hd * hd))
+            return table.get(key)
+
+        def table(kern, tag, T):
+            out = {}
+            for (tg, key), v in kern.items():
+                if tg != tag:
+                    continue
+                t = med(v)
+                e = {"us": round(t * 1e6, 1), "calls_per_step": len(v)}
+                w = work(tag, key, T)
+                if w:
+                    roof = w[1] / {"bytes": HBM, "flops": TC, "f32": F32}[w[0]]
+                    e.update(bound=w[0], roofline_us=round(roof * 1e6, 2), frac_of_roofline=round(roof / t, 3))
+                out[key] = e
+            return out
+        results[name] = {
+            "panarax": {"prefill_tokens_per_s": round(P / p_pre), "prefill_ms": round(p_pre * 1e3, 2), "decode_tokens_per_s": round(B / p_dec),
+                        "decode_ms_per_step": round(p_dec * 1e3, 3), "decode": "CUDA-graph replay incl. host metadata and H2D",
+                        "decode_ms_per_step_device": round(p_dec_dev * 1e3, 3), "decode_tokens_per_s_device": round(B / p_dec_dev),
+                        "kernels_prefill": table(p_kern, "prefill", P), "kernels_decode": table(p_kern, "decode", B)},
+            "gobesun": {"prefill_tokens_per_s": round(P / g_pre), "prefill_ms": round(g_pre * 1e3, 2), "decode_tokens_per_s": round(B / g_dec),
+                        "decode_ms_per_step": round(g_dec * 1e3, 3), "decode_ms_per_step_device": round(g_dec_dev * 1e3, 3),
+                        "decode_tokens_per_s_device": round(B / g_dec_dev),
+                        "kernels_prefill": table(g_kern, "prefill", P), "kernels_decode": table(g_kern, "decode", B)},
+            "shape": dict(z, prompt=P, decode_batch=B, decode_ctx=CTX, head_dim=hd, recurrence_blocks=H, memory_heads=Hm),
+        }
+    clocks = sampler.stop()
+    first = results[next(iter(results))]
+    print(json.dumps({"metric": "Panarax prefill / decode tokens/s beside a Gobesun of equal size", "value": first["panarax"]["decode_tokens_per_s"],
+                      "unit": UNIT, "n_gpus": 1, "steps": K, "warmup": W, "higher_is_better": True, "dtype": "bf16", "data": "synthetic", "arch": "panarax",
+                      "peaks": {"hbm_gbs": peaks["hbm_gbs"], "bf16_tflops": peaks["bf16_tflops"], "f32_fma_tflops_nominal": round(F32 / 1e12, 1),
+                                "source": "fallback" if peaks.get("fallback") else "MEASURED_PEAKS.json"},
+                      "l2": "weights and activations of a step exceed L2 (126 MB)", "clocks": clocks,
+                      "gpu_launches": int(pkg.lib().b200_total_kernel_launches() - l0), "sizes": results}))
+
+
 def main():
     args = parse()
     if args.arch == "gobesun":
         run_gobesun(args)
+        return
+    if args.arch == "panarax":
+        run_panarax(args)
         return
     if args.arch == "guvusun":
         run_guvusun(args)

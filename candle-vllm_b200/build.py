@@ -40,10 +40,10 @@ GROUPS = {"ragged": ["lib", "linear_generic", "dense_gemm", "norm_act", "gated_d
           # split-KV latent decode kernel, the expert kernels, argmax
           "latent": ["lib", "linear_generic", "dense_gemm", "norm_act", "latent_attention", "moe_ragged", "mla", "elementwise"],
           # state-space / linear-attention mixers beside softmax attention, with dense or routed feed-forwards: both linear kernels (the tcgen05 one also
-          # grouped), norms, the recurrences, the SIMT attention over the paged cache and the tensor-core prefill kernel it hands 128-wide heads to, the
-          # head gate of the latent mixers, the expert kernels
-          "hybrid": ["lib", "linear_generic", "dense_gemm", "norm_act", "linear_recurrence", "attention_varlen", "attention_prefill", "latent_attention",
-                     "moe_ragged", "elementwise"]}
+          # grouped), norms, the recurrences, the SIMT attention over the paged cache and the tensor-core prefill and split-KV decode kernels it hands 128-wide
+          # heads to, the expert kernels
+          "hybrid": ["lib", "linear_generic", "dense_gemm", "norm_act", "linear_recurrence", "attention_varlen", "attention_prefill", "attention_decode",
+                     "attention_generic", "attention_api", "moe_ragged", "elementwise"]}
 
 
 def so_path(group=None) -> str:

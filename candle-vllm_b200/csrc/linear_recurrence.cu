@@ -8,7 +8,8 @@
 //   block_diag_linear     out[t, b M + j] = sum_i w[b, j, i] x[t, b N + i] + bias[b M + j]: one matrix per block of N neighbouring
 //                         channels, true 32-bit products (the gates of a recurrence).
 //   gated_linear_scan     per channel  S_t = a_t S_(t-1) + sqrt(1 - a_t^2) i_t u_t,  a_t = exp(-c r_t softplus(lam)),  r, i = sigmoid of
-//                         the block-diagonal products;  out_t = S_t * gelu_tanh(y_t + y_bias).
+//                         the block-diagonal products;  out_t = S_t * gelu_tanh(y_t + y_bias).  One kernel for steps of few rows per entry;
+//                         for portions of prompts a row-parallel pass first turns gates and y into a_t, the input term and the GELU (in place).
 //   linear_attention      per head, S [dk, dv]:  S_t = a_t S_(t-1) + b_t k_t v_t^T,  o_t = S_t^T q_t, in two gatings:
 //                           fixed decay      a = decay[h], b = 1;
 //                           exponential      a_t = e^(f_t + m_(t-1) - m_t), b_t = e^(i_t - m_t) with the running maximum m_t = max(f_t + m_(t-1), i_t),
@@ -219,8 +220,70 @@ gated_linear_scan_kernel(const float* __restrict__ u, int64_t ldu, const float* 
     *sp = S;
 }
 
+// Portions of prompts: the per-token part (two sigmoids, the decay and its square-root complement, the GELU of the other branch) is done for all
+// rows at once, in place -- gates[t, blk, j] <- a_t, gates[t, blk, n + j] <- sqrt(1 - a_t^2) i_t u_t, y[t, c] <- gelu_tanh(y + bias) -- and the scan
+// itself is two multiply-adds per row with the next rows' operands in flight.
+__global__ void gated_scan_prepare_kernel(const float* __restrict__ u, int64_t ldu, float* __restrict__ gates, int64_t ldg, const float* __restrict__ lam,
+                                          float* __restrict__ y, int64_t ldy, const float* __restrict__ y_bias, int64_t rows, int C, int n, float decay_scale) {
+    pdl_wait();
+    pdl_trigger();
+    const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= rows * C) return;
+    const int64_t t = i / C;
+    const int c = (int)(i - t * C);
+    const int blk = c / n, j = c - blk * n;
+    float* gr = gates + t * ldg + blk * 2 * n + j;
+    const float la = -decay_scale * softplus_f(lam[c]) * sigmoid_f(gr[0]);
+    const float b = sqrtf(-expm1f(2.0f * la)) * sigmoid_f(gr[n]) * u[t * ldu + c];
+    gr[0] = expf(la);
+    gr[n] = b;
+    y[t * ldy + c] = gelu_tanh_f(y[t * ldy + c] + (y_bias ? y_bias[c] : 0.f));
+}
+
+template <typename TOut>
+__global__ void __launch_bounds__(32)
+linear_scan_kernel(const float* __restrict__ gates, int64_t ldg, const float* __restrict__ y, int64_t ldy, float* __restrict__ state, TOut* __restrict__ out,
+                   const int32_t* __restrict__ cu_seqlens, const int32_t* __restrict__ seq_slots, const int32_t* __restrict__ seq_start, int C, int n) {
+    pdl_wait();
+    pdl_trigger();
+    const int c = blockIdx.x * 32 + threadIdx.x;
+    const int b = blockIdx.y;
+    if (c >= C) return;
+    const int t0 = cu_seqlens[b], t1 = cu_seqlens[b + 1];
+    if (t1 <= t0) return;
+    float* sp = state + (int64_t)seq_slots[b] * C + c;
+    float S = seq_start[b] == 0 ? 0.f : *sp;
+    const int blk = c / n, j = c - blk * n;
+    const float* ga = gates + blk * 2 * n + j;
+    constexpr int kAhead = 16;
+    float na[kAhead], nb[kAhead], ny[kAhead];
+#pragma unroll
+    for (int a = 0; a < kAhead; ++a) {
+        const int64_t t = min(t0 + a, t1 - 1);
+        na[a] = ga[t * ldg]; nb[a] = ga[t * ldg + n]; ny[a] = y[t * ldy + c];
+    }
+    for (int tb = t0; tb < t1; tb += kAhead) {
+        float ca[kAhead], cb[kAhead], cy[kAhead];
+#pragma unroll
+        for (int a = 0; a < kAhead; ++a) { ca[a] = na[a]; cb[a] = nb[a]; cy[a] = ny[a]; }
+#pragma unroll
+        for (int a = 0; a < kAhead; ++a) {
+            const int64_t t = min(tb + kAhead + a, t1 - 1);
+            na[a] = ga[t * ldg]; nb[a] = ga[t * ldg + n]; ny[a] = y[t * ldy + c];
+        }
+#pragma unroll
+        for (int a = 0; a < kAhead; ++a) {
+            if (tb + a >= t1) break;
+            S = fmaf(ca[a], S, cb[a]);
+            out[(int64_t)(tb + a) * C + c] = from_f32<TOut>(S * cy[a]);
+        }
+    }
+    *sp = S;
+}
+
 // ---- linear attention with a matrix state ---------------------------------------------------------------------------------------------
 constexpr int kTile = 16;
+constexpr int kScanSplitRows = 16;     // entries with at least this many rows: the gated scan runs as a row-parallel pass plus a bare scan
 
 struct LinAttnArgs {
     const float* proj; int64_t ld;
@@ -247,7 +310,7 @@ linear_attention_kernel(const LinAttnArgs A) {
     float* sa = sv + kTile * 16;                 // [kTile] decay of the state
     float* sb = sa + kTile;                      // [kTile] weight of the new outer product
     float* se = sb + kTile;                      // [kTile] e^(-m_t)
-    float* sf = se + kTile;                      // [kTile] f_t, then scratch
+    float* sf = se + kTile;                      // [kTile] f_t
     float* si = sf + kTile;                      // [kTile] i_t
     float* sm = si + kTile;                      // [kTile + 1] m before the tile's first token, then m_t
     const int h = blockIdx.y, b = blockIdx.z;
@@ -261,47 +324,75 @@ linear_attention_kernel(const LinAttnArgs A) {
     const bool col_ok = col < dv;
     const bool fresh = A.seq_start[b] == 0;
     const int64_t slot = A.seq_slots[b];
+    const bool vec = (dk & 3) == 0;              // a lane's rows of the state are then whole 16-byte words
     float* Sp = A.S + ((slot * H + h) * dv + (col_ok ? col : 0)) * (int64_t)dk + part * kR;
     // the normaliser and the maximum are kept once per block of 16 columns: every block reads and writes a copy of its own
     const int64_t own = (slot * H + h) * (int64_t)gridDim.x + blockIdx.x;
     float* np = kExp ? A.nrm + own * dk + part * kR : nullptr;
     float S[kR], nv[kR];
 #pragma unroll
-    for (int r = 0; r < kR; ++r) {
-        const bool ok = part * kR + r < dk;
-        S[r] = (!fresh && col_ok && ok) ? Sp[r] : 0.f;
-        nv[r] = (kExp && !fresh && ok) ? np[r] : 0.f;
+    for (int r = 0; r < kR; ++r) { S[r] = 0.f; nv[r] = 0.f; }
+    if (!fresh) {
+        if (vec) {
+#pragma unroll
+            for (int r4 = 0; r4 < kR / 4; ++r4) {
+                if (part * kR + r4 * 4 >= dk) continue;
+                if (col_ok) { const float4 v = reinterpret_cast<const float4*>(Sp)[r4]; S[r4 * 4] = v.x; S[r4 * 4 + 1] = v.y; S[r4 * 4 + 2] = v.z; S[r4 * 4 + 3] = v.w; }
+                if (kExp) { const float4 v = reinterpret_cast<const float4*>(np)[r4]; nv[r4 * 4] = v.x; nv[r4 * 4 + 1] = v.y; nv[r4 * 4 + 2] = v.z; nv[r4 * 4 + 3] = v.w; }
+            }
+        } else {
+#pragma unroll
+            for (int r = 0; r < kR; ++r) {
+                const bool ok = part * kR + r < dk;
+                if (col_ok && ok) S[r] = Sp[r];
+                if (kExp && ok) nv[r] = np[r];
+            }
+        }
     }
     if (kExp && threadIdx.x == 0) sm[0] = fresh ? 0.f : A.mx[own];
     const float fixed_a = kExp ? 0.f : A.decay[h];
+    // the next tile's operands travel in registers while the current tile is walked: element e = thread + 128 i of the tile's [16][kP] q and k
+    // rows, two of its [16][16] values, and (lanes 0..15 of the last warp) the two gate pre-activations of a token
+    float pq[kR], pk[kR], pv[2], pgi = 0.f, pgf = 0.f;
+    auto fetch = [&](int tb) {
+        const int nt = min(kTile, t1 - tb);
+#pragma unroll
+        for (int i = 0; i < kR; ++i) {
+            const int e = threadIdx.x + 128 * i, tt = e / kP, r = e - tt * kP;
+            const bool ok = tt < nt && r < dk;
+            const float* row = A.proj + (int64_t)(tb + (ok ? tt : 0)) * A.ld;
+            pq[i] = ok ? row[A.off_q + h * dk + r] : 0.f;
+            pk[i] = ok ? row[A.off_k + h * dk + r] : 0.f;
+        }
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+            const int e = threadIdx.x + 128 * i, tt = e >> 4, gc = blockIdx.x * 16 + (e & 15);
+            pv[i] = (tt < nt && gc < dv) ? A.proj[(int64_t)(tb + tt) * A.ld + A.off_v + h * dv + gc] : 0.f;
+        }
+        if (kExp && warp == 3 && lane < nt) {
+            const float* row = A.proj + (int64_t)(tb + lane) * A.ld;
+            pgi = row[A.off_i + h] + (A.i_bias ? A.i_bias[h] : 0.f);
+            pgf = row[A.off_f + h] + (A.f_bias ? A.f_bias[h] : 0.f);
+        }
+    };
+    fetch(t0);
     for (int tb = t0; tb < t1; tb += kTile) {
         const int nt = min(kTile, t1 - tb);
         __syncthreads();                         // the previous tile has been walked
-        for (int e = threadIdx.x; e < nt * kP; e += 128) {
-            const int tt = e / kP, r = e - tt * kP;
-            float qv = 0.f, kv = 0.f;
-            if (r < dk) {
-                const float* row = A.proj + (int64_t)(tb + tt) * A.ld;
-                qv = row[A.off_q + h * dk + r]; kv = row[A.off_k + h * dk + r];
-                if (A.act == 1) { qv = silu_f(qv); kv = silu_f(kv); }
-                qv *= A.q_scale;
-            }
-            sq[tt * kP + r] = qv; sk[tt * kP + r] = kv;
+#pragma unroll
+        for (int i = 0; i < kR; ++i) {
+            const int e = threadIdx.x + 128 * i;
+            float qv = pq[i], kv = pk[i];
+            if (A.act == 1) { qv = silu_f(qv); kv = silu_f(kv); }
+            sq[e] = qv * A.q_scale; sk[e] = kv;
         }
-        for (int e = threadIdx.x; e < nt * 16; e += 128) {
-            const int tt = e >> 4, c = e & 15;
-            const int gc = blockIdx.x * 16 + c;
-            float v = 0.f;
-            if (gc < dv) { v = A.proj[(int64_t)(tb + tt) * A.ld + A.off_v + h * dv + gc]; if (A.act == 1) v = silu_f(v); }
-            sv[e] = v;
-        }
+#pragma unroll
+        for (int i = 0; i < 2; ++i) sv[threadIdx.x + 128 * i] = A.act == 1 ? silu_f(pv[i]) : pv[i];
         if (kExp && warp == 3) {
             // gate values of the tile's tokens, the chain of maxima, then the coefficients
             if (lane < nt) {
-                const float* row = A.proj + (int64_t)(tb + lane) * A.ld;
-                const float zi = row[A.off_i + h] + (A.i_bias ? A.i_bias[h] : 0.f), zf = row[A.off_f + h] + (A.f_bias ? A.f_bias[h] : 0.f);
-                si[lane] = A.cap * tanhf(zi / A.cap);
-                sf[lane] = log_sigmoid_f(A.cap * tanhf(zf / A.cap));
+                si[lane] = A.cap * tanhf(pgi / A.cap);
+                sf[lane] = log_sigmoid_f(A.cap * tanhf(pgf / A.cap));
             }
             __syncwarp();
             if (lane == 0) {
@@ -317,11 +408,12 @@ linear_attention_kernel(const LinAttnArgs A) {
             }
         }
         __syncthreads();
+        if (tb + kTile < t1) fetch(tb + kTile);
         for (int tt = 0; tt < nt; ++tt) {
             const float a = kExp ? sa[tt] : fixed_a;
             const float bv = (kExp ? sb[tt] : 1.0f) * sv[tt * 16 + colb];
             const float bn = kExp ? sb[tt] : 0.f;
-            float acc = 0.f, nq = 0.f;
+            float acc[2] = {0.f, 0.f}, nq[2] = {0.f, 0.f};
             const float4* q4 = reinterpret_cast<const float4*>(sq + tt * kP + part * kR);
             const float4* k4 = reinterpret_cast<const float4*>(sk + tt * kP + part * kR);
 #pragma unroll
@@ -332,18 +424,18 @@ linear_attention_kernel(const LinAttnArgs A) {
                 for (int j = 0; j < 4; ++j) {
                     const int r = r4 * 4 + j;
                     S[r] = fmaf(a, S[r], ka[j] * bv);
-                    acc = fmaf(S[r], qa[j], acc);
-                    if (kExp) { nv[r] = fmaf(a, nv[r], ka[j] * bn); nq = fmaf(nv[r], qa[j], nq); }
+                    acc[j & 1] = fmaf(S[r], qa[j], acc[j & 1]);
+                    if (kExp) { nv[r] = fmaf(a, nv[r], ka[j] * bn); nq[j & 1] = fmaf(nv[r], qa[j], nq[j & 1]); }
                 }
             }
+            float o = acc[0] + acc[1], nqs = nq[0] + nq[1];
 #pragma unroll
-            for (int o = 4; o < 32; o <<= 1) {
-                acc += __shfl_xor_sync(0xffffffffu, acc, o);
-                if (kExp) nq += __shfl_xor_sync(0xffffffffu, nq, o);
+            for (int sh = 4; sh < 32; sh <<= 1) {
+                o += __shfl_xor_sync(0xffffffffu, o, sh);
+                if (kExp) nqs += __shfl_xor_sync(0xffffffffu, nqs, sh);
             }
             if (part == 0 && col_ok) {
-                float o = acc;
-                if (kExp) o = acc / (fmaxf(fabsf(nq), se[tt]) + 1e-6f);
+                if (kExp) o = o / (fmaxf(fabsf(nqs), se[tt]) + 1e-6f);
                 A.out[(int64_t)(tb + tt) * H * dv + h * dv + col] = o;
             }
         }
@@ -352,11 +444,20 @@ linear_attention_kernel(const LinAttnArgs A) {
             if (threadIdx.x == 0) sm[0] = sm[nt];
         }
     }
+    if (vec) {
 #pragma unroll
-    for (int r = 0; r < kR; ++r) {
-        const bool ok = part * kR + r < dk;
-        if (col_ok && ok) Sp[r] = S[r];
-        if (kExp && ok && warp == 0 && cl == 0) np[r] = nv[r];
+        for (int r4 = 0; r4 < kR / 4; ++r4) {
+            if (part * kR + r4 * 4 >= dk) continue;
+            if (col_ok) reinterpret_cast<float4*>(Sp)[r4] = make_float4(S[r4 * 4], S[r4 * 4 + 1], S[r4 * 4 + 2], S[r4 * 4 + 3]);
+            if (kExp && warp == 0 && cl == 0) reinterpret_cast<float4*>(np)[r4] = make_float4(nv[r4 * 4], nv[r4 * 4 + 1], nv[r4 * 4 + 2], nv[r4 * 4 + 3]);
+        }
+    } else {
+#pragma unroll
+        for (int r = 0; r < kR; ++r) {
+            const bool ok = part * kR + r < dk;
+            if (col_ok && ok) Sp[r] = S[r];
+            if (kExp && ok && warp == 0 && cl == 0) np[r] = nv[r];
+        }
     }
     if (kExp) {
         __syncthreads();
@@ -428,22 +529,38 @@ void block_diag_linear(const float* x, int64_t ldx, const float* weight, const f
     check_launch("block_diag_linear");
 }
 
-void gated_linear_scan(const float* u, int64_t ldu, const float* gates, int64_t ld_gates, const float* lam, const float* y_pre, int64_t ldy, const float* y_bias,
-                       float* state, void* out, const int32_t* cu_seqlens, const int32_t* seq_slots, const int32_t* seq_start, int32_t num_seqs, int32_t channels,
-                       int32_t block_channels, float decay_scale, int32_t out_dtype, int64_t stream) {
-    if (num_seqs == 0) return;
+void gated_linear_scan(const float* u, int64_t ldu, float* gates, int64_t ld_gates, const float* lam, float* y_pre, int64_t ldy, const float* y_bias,
+                       float* state, void* out, const int32_t* cu_seqlens, const int32_t* seq_slots, const int32_t* seq_start, int32_t num_tokens, int32_t num_seqs,
+                       int32_t max_rows, int32_t channels, int32_t block_channels, float decay_scale, int32_t out_dtype, int64_t stream) {
+    if (num_seqs == 0 || num_tokens == 0) return;
     B200_REQUIRE(u && gates && lam && y_pre && state && out && cu_seqlens && seq_slots && seq_start && channels > 0 && block_channels > 0 &&
                  channels % block_channels == 0 && ldu >= channels && ldy >= channels && ld_gates >= 2 * (int64_t)channels && num_seqs <= 65535, kErrBadArg,
                  "gated_linear_scan: bad arguments");
+    B200_REQUIRE(out_dtype == B200_F32 || out_dtype == B200_BF16, kErrUnsupported, "gated_linear_scan: out dtype %d (f32 / bf16)", out_dtype);
     cudaStream_t st = as_stream(stream);
+    if (max_rows >= kScanSplitRows) {
+        // portions of prompts: everything but the recurrence itself for all rows at once (in place), then a scan of two multiply-adds per row
+        const int64_t total = (int64_t)num_tokens * channels;
+        launch_pdl(gated_scan_prepare_kernel, dim3((unsigned)((total + 255) / 256)), dim3(256), 0, st, u, ldu, gates, ld_gates, lam, y_pre, ldy, y_bias,
+                   (int64_t)num_tokens, channels, block_channels, decay_scale);
+        const dim3 grid(ceil_div(channels, 32), num_seqs);
+        if (out_dtype == B200_F32)
+            launch_pdl(linear_scan_kernel<float>, grid, dim3(32), 0, st, (const float*)gates, ld_gates, (const float*)y_pre, ldy, state, (float*)out, cu_seqlens, seq_slots,
+                       seq_start, channels, block_channels);
+        else
+            launch_pdl(linear_scan_kernel<__nv_bfloat16>, grid, dim3(32), 0, st, (const float*)gates, ld_gates, (const float*)y_pre, ldy, state, (__nv_bfloat16*)out,
+                       cu_seqlens, seq_slots, seq_start, channels, block_channels);
+        count_launch(2);
+        check_launch("gated_linear_scan");
+        return;
+    }
     const dim3 grid(ceil_div(channels, 64), num_seqs);
     if (out_dtype == B200_F32)
-        launch_pdl(gated_linear_scan_kernel<float>, grid, dim3(64), 0, st, u, ldu, gates, ld_gates, lam, y_pre, ldy, y_bias, state, (float*)out, cu_seqlens, seq_slots,
-                   seq_start, channels, block_channels, decay_scale);
-    else if (out_dtype == B200_BF16)
-        launch_pdl(gated_linear_scan_kernel<__nv_bfloat16>, grid, dim3(64), 0, st, u, ldu, gates, ld_gates, lam, y_pre, ldy, y_bias, state, (__nv_bfloat16*)out,
+        launch_pdl(gated_linear_scan_kernel<float>, grid, dim3(64), 0, st, u, ldu, (const float*)gates, ld_gates, lam, (const float*)y_pre, ldy, y_bias, state, (float*)out,
                    cu_seqlens, seq_slots, seq_start, channels, block_channels, decay_scale);
-    else { set_error(kErrUnsupported, "gated_linear_scan: out dtype %d (f32 / bf16)", out_dtype); return; }
+    else
+        launch_pdl(gated_linear_scan_kernel<__nv_bfloat16>, grid, dim3(64), 0, st, u, ldu, (const float*)gates, ld_gates, lam, (const float*)y_pre, ldy, y_bias, state,
+                   (__nv_bfloat16*)out, cu_seqlens, seq_slots, seq_start, channels, block_channels, decay_scale);
     count_launch();
     check_launch("gated_linear_scan");
 }

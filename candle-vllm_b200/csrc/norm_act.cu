@@ -18,7 +18,8 @@
 //                    g' = min(g, limit), u' = clamp(u, +-limit), g' sigmoid(1.702 g') (u' + 1); a per-row factor may multiply gate and
 //                    up first (an expert that sees its token times the router's score);
 //   group_rms_norm_gate  out = o / rms(o over a group of neighbours) * w * act(gate): the closing norm of the linear-attention mixers,
-//                    one group per head or one for the whole row.
+//                    one group per head or one for the whole row;
+//   head_gate        out[t, h, :] = src[t, h, :] * sigmoid(gate[t, h]): one gate per attention head.
 // Any row length (no vector-width rule): the rows these models use are a few hundred to a few thousand floats and every kernel
 // here is one pass over them from L2.
 #include "common.cuh"
@@ -265,6 +266,19 @@ group_rms_norm_gate_kernel(const float* __restrict__ o, int64_t ldo, const float
     }
 }
 
+
+template <typename TS, typename TOut>
+__global__ void head_gate_kernel(const TS* __restrict__ src, const float* __restrict__ gate, int64_t ldg, TOut* __restrict__ out, int64_t rows, int H, int dv) {
+    pdl_wait();
+    pdl_trigger();
+    const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    const int64_t n = (int64_t)H * dv;
+    if (i >= rows * n) return;
+    const int64_t r = i / n;
+    const int h = (int)((i - r * n) / dv);
+    out[i] = from_f32<TOut>(to_f32<TS>(src[i]) / (1.0f + expf(-gate[r * ldg + h])));
+}
+
 }  // namespace
 }  // namespace b200
 
@@ -425,6 +439,23 @@ void group_rms_norm_gate(const float* o, int64_t ldo, const float* weight, const
     else { set_error(kErrUnsupported, "group_rms_norm_gate: out dtype %d (f32 / bf16)", out_dtype); return; }
     count_launch();
     check_launch("group_rms_norm_gate");
+}
+
+void head_gate(const void* src, int32_t src_dtype, const float* gate, int64_t ld_gate, void* out, int32_t out_dtype, int32_t num_tokens, int32_t num_heads, int32_t dv,
+               int64_t stream) {
+    if (num_tokens == 0) return;
+    B200_REQUIRE(src && gate && out && num_heads > 0 && dv > 0 && ld_gate >= num_heads, kErrBadArg, "head_gate: bad arguments");
+    const int64_t total = (int64_t)num_tokens * num_heads * dv;
+    const unsigned grid = (unsigned)((total + 255) / 256);
+    cudaStream_t st = as_stream(stream);
+#define HG(TS, TO) launch_pdl(head_gate_kernel<TS, TO>, dim3(grid), dim3(256), 0, st, (const TS*)src, gate, ld_gate, (TO*)out, (int64_t)num_tokens, num_heads, dv)
+    if (src_dtype == B200_F32 && out_dtype == B200_F32) HG(float, float);
+    else if (src_dtype == B200_F32 && out_dtype == B200_BF16) HG(float, __nv_bfloat16);
+    else if (src_dtype == B200_BF16 && out_dtype == B200_BF16) HG(__nv_bfloat16, __nv_bfloat16);
+    else { set_error(kErrUnsupported, "head_gate: source dtype %d / out dtype %d", src_dtype, out_dtype); return; }
+#undef HG
+    count_launch();
+    check_launch("head_gate");
 }
 
 }  // extern "C"

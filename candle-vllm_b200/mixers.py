@@ -112,9 +112,9 @@ class PagedAttentionMixer:
         if self.rot_dims % 2 or self.rot_dims > dk:
             raise BackendError(f"PagedAttentionMixer: {self.rot_dims} rotary dims do not fit a head of {dk}")
         # 16-bit q for the tensor-core attention kernel (128-wide heads, 64-token blocks, bf16 cache); f32 q for the SIMT one
-        self.q_dtype = torch.bfloat16 if (dtype == torch.bfloat16 and dk == dv == 128 and block_size == 64 and not self.has_gate) else torch.float32
+        self.q_dtype = torch.bfloat16 if (dtype == torch.bfloat16 and dk == dv == 128 and block_size == 64) else torch.float32
         # steps of single tokens: the split-KV decode kernel, when chunks start on block borders and the head layout is one it takes
-        self.decode_kernel = (self.q_dtype == torch.bfloat16 and self.chunk > 0 and self.chunk % block_size == 0 and heads // kv_heads in (1, 2, 4, 8))
+        self.decode_kernel = (self.q_dtype == torch.bfloat16 and self.chunk % block_size == 0 and self.window == 0 and heads // kv_heads in (1, 2, 4, 8))
         self._scratch = {}
         self.cos = self.sin = None
         self._device = self.w_in.device
@@ -137,17 +137,17 @@ class PagedAttentionMixer:
             proj = ops.linear(h, self.w_in)
         q = ops.qk_norm_rope_cache(proj, self.q_norm, self.k_norm, self.cos, self.sin, batch, k_cache, v_cache, self.H, self.G, self.dk, self.dv,
                                    self.rot_dims, self.eps, self.q_dtype, q_temp=self.q_temp, v_unit_rms=self.value_norm)
-        if self.has_gate:
-            # the head outputs stay f32 until the gate has been applied, then take the compute dtype once
-            a = ops.paged_attention_varlen(q, k_cache, v_cache, batch, self.H, self.G, self.dk, self.dv, self.block_size, self.scale, self.chunk,
-                                           self.window, torch.float32)
-            a = ops.latent_out_gate(a.view(-1, self.H, self.dv), None, proj[:, self.off_g:], self.H, self.dv, self.dv, self.dtype)
-            return ops.linear(a, self.w_o)
         if self.decode_kernel and batch.pure_decode and batch.num_seqs <= 256:
-            a = ops.paged_attention_decode_chunked(q, k_cache, v_cache, batch, self.H, self.G, self.dk, self.block_size, self.scale, self.chunk, self._scratch)
+            # without a chunk mask the whole table is one chunk
+            a = ops.paged_attention_decode_chunked(q, k_cache, v_cache, batch, self.H, self.G, self.dk, self.block_size, self.scale,
+                                                   self.chunk or batch.block_tables.shape[1] * self.block_size, self._scratch)
         else:
+            # on the SIMT kernel gated head outputs stay f32 until the gate has been applied and take the compute dtype once; the tensor-core kernel
+            # (16-bit q) returns 16 bits
             a = ops.paged_attention_varlen(q, k_cache, v_cache, batch, self.H, self.G, self.dk, self.dv, self.block_size, self.scale, self.chunk,
-                                           self.window, self.dtype)
+                                           self.window, torch.float32 if (self.has_gate and self.q_dtype == torch.float32) else self.dtype)
+        if self.has_gate:
+            a = ops.head_gate(a, proj[:, self.off_g:], self.H, self.dv, self.dtype)
         return ops.linear(a, self.w_o)
 
 

@@ -211,6 +211,8 @@ def paged_attention_decode_chunked(q: torch.Tensor, k_cache: torch.Tensor, v_cac
     width = chunk // block_size
     key = (B, width)
     if key not in scratch:
+        if len(scratch) >= 8:                   # tables that grow step by step: keep a few views, not one per width ever seen
+            scratch.clear()
         need = lib().paged_attention_decode_workspace_bytes(C.c_int32(B), C.c_int32(heads), C.c_int32(hd), C.c_int32(width), C.c_int32(block_size))
         scratch[key] = (torch.zeros((B, width), dtype=torch.int32, device=q.device), torch.zeros(B, dtype=torch.int32, device=q.device),
                         torch.zeros(int(need), dtype=torch.uint8, device=q.device))
@@ -563,6 +565,18 @@ def group_rms_norm_gate(o: torch.Tensor, weight: Optional[torch.Tensor], gate: O
     return out
 
 
+def head_gate(src: torch.Tensor, gate: torch.Tensor, heads: int, dv: int, out_dtype: torch.dtype) -> torch.Tensor:
+    """src [T, H dv] (f32 or bf16, contiguous) times sigmoid(gate[t, h]) (f32 view [T, H], row stride allowed) -> [T, H dv] of ``out_dtype``"""
+    T = src.shape[0]
+    if not src.is_contiguous() or src.shape[1] != heads * dv or gate.dtype != torch.float32 or gate.stride(1) != 1:
+        raise BackendError(f"head_gate: src {tuple(src.shape)}, gate {tuple(gate.shape)} {gate.dtype}")
+    out = torch.empty((T, heads * dv), dtype=out_dtype, device=src.device)
+    lib().head_gate(_ptr(src), C.c_int32(_tag(src.dtype)), _ptr(gate), C.c_int64(gate.stride(0) if T > 1 else max(heads, gate.stride(0))), _ptr(out), C.c_int32(_tag(out_dtype)),
+                    C.c_int32(T), C.c_int32(heads), C.c_int32(dv), _stream(src.device))
+    check("head_gate")
+    return out
+
+
 def causal_conv(x: torch.Tensor, taps: torch.Tensor, conv_state: torch.Tensor, batch: StepBatch, out_dtype: torch.dtype = torch.float32,
                 in_bias: Optional[torch.Tensor] = None, out_bias: Optional[torch.Tensor] = None, act: str = "none", add_input: bool = False) -> torch.Tensor:
     """Causal convolution over time on each channel of x (f32 view [T, C], row stride allowed): act(taps * inputs + out_bias) (+ the input itself), the
@@ -598,13 +612,13 @@ def block_diag_linear(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torc
 def gated_linear_scan(u: torch.Tensor, gates: torch.Tensor, lam: torch.Tensor, y_pre: torch.Tensor, y_bias: Optional[torch.Tensor], state: torch.Tensor, batch: StepBatch,
                       block_channels: int, decay_scale: float, out_dtype: torch.dtype) -> torch.Tensor:
     """u f32 [T, C]; gates f32 [T, blocks, 2 n] (recurrence gate, then input gate, per block); y_pre f32 view [T, C]; state f32 [slots, C] advanced in place
-    -> S_t * gelu_tanh(y_pre + y_bias) of ``out_dtype``"""
+    -> S_t * gelu_tanh(y_pre + y_bias) of ``out_dtype``.  ``gates`` and ``y_pre`` are scratch: steps with portions of prompts overwrite them."""
     T, Cn = u.shape
     out = torch.empty((T, Cn), dtype=out_dtype, device=u.device)
     pitch = lambda t, n: t.stride(0) if T > 1 else max(n, t.stride(0))
     lib().gated_linear_scan(_ptr(u), C.c_int64(pitch(u, Cn)), _ptr(gates), C.c_int64(pitch(gates, 2 * Cn)), _ptr(lam), _ptr(y_pre), C.c_int64(pitch(y_pre, Cn)), _ptr(y_bias),
-                            _ptr(state), _ptr(out), _ptr(batch.cu_seqlens), _ptr(batch.seq_slots), _ptr(batch.seq_start), C.c_int32(batch.num_seqs), C.c_int32(Cn),
-                            C.c_int32(block_channels), C.c_float(decay_scale), C.c_int32(_tag(out_dtype)), _stream(u.device))
+                            _ptr(state), _ptr(out), _ptr(batch.cu_seqlens), _ptr(batch.seq_slots), _ptr(batch.seq_start), C.c_int32(T), C.c_int32(batch.num_seqs),
+                            C.c_int32(batch.max_rows), C.c_int32(Cn), C.c_int32(block_channels), C.c_float(decay_scale), C.c_int32(_tag(out_dtype)), _stream(u.device))
     check("gated_linear_scan")
     return out
 

@@ -329,3 +329,90 @@ def guvusun_weights(cfg: dict, seed: int = 0, device="cpu") -> dict:
         if side:
             out[p + "side.gate"], out[p + "side.proj"], out[p + "side.norm"] = lin(side, D), lin(D, side), 0.5 + rnd(D, std=0.1)
     return {k: v.to(torch.bfloat16).to(device) for k, v in out.items()}
+
+
+# ---------------------------------------------------------------------------------------------------------------------
+# Panarax: random checkpoints of any shape (tests and bench.py)
+# ---------------------------------------------------------------------------------------------------------------------
+def _panarax_mlp(ff: int, experts: int, top: int, limit: float):
+    if not ff:
+        return None
+    if experts:
+        return dict(kind="moe", expert=dict(ff=ff, limit=limit), router=dict(experts=experts, top=top))
+    return dict(kind="dense", ff=ff)
+
+
+def panarax_rglru_layer(width: int, blocks: int, conv: int = 4, ff: int = 0, experts: int = 0, top: int = 1, limit: float = 7.0) -> dict:
+    return dict(type="rglru", mixer=dict(width=width, blocks=blocks, conv=conv), mlp=_panarax_mlp(ff, experts, top, limit))
+
+
+def panarax_lightning_layer(heads: int, dim: int, vdim: int, decay=None, ff: int = 0, experts: int = 0, top: int = 1, limit: float = 7.0) -> dict:
+    decay = list(decay) if decay is not None else [1.0 - 2.0 ** (-1.5 - 6.0 * h / max(heads - 1, 1)) for h in range(heads)]
+    return dict(type="lightning", mixer=dict(heads=heads, dim=dim, vdim=vdim, decay=decay), mlp=_panarax_mlp(ff, experts, top, limit))
+
+
+def panarax_parallel_layer(heads: int, kv_heads: int, dim: int, vdim: int, m_heads: int, m_dim: int, m_vdim: int, q_temp=(0.2, 32), gate_cap: float = 12.0,
+                           scale: float = None, ff: int = 0, experts: int = 0, top: int = 1, limit: float = 7.0) -> dict:
+    left = dict(heads=heads, kv_heads=kv_heads, dim=dim, vdim=vdim, scale=dim ** -0.5 if scale is None else scale)
+    if q_temp:
+        left["q_temp"] = dict(coef=q_temp[0], every=q_temp[1])
+    return dict(type="parallel", mixer=dict(left=left, right=dict(heads=m_heads, dim=m_dim, vdim=m_vdim, gate_cap=gate_cap)), mlp=_panarax_mlp(ff, experts, top, limit))
+
+
+def panarax_config(width: int, vocab: int, layers: list, max_positions: int = 4096, taps: int = 3, eps: float = 1e-6) -> dict:
+    return dict(architecture="Panarax", canon=dict(taps=taps), layers=layers, max_positions=max_positions, norm=dict(eps=eps), vocab=vocab, width=width)
+
+
+def panarax_weights(cfg: dict, seed: int = 0, device="cpu") -> dict:
+    """name -> bf16 tensor, with the magnitudes of a model at initialisation (unit-variance activations through every sublayer)."""
+    g = torch.Generator().manual_seed(seed)
+    D, K = cfg["width"], cfg["canon"]["taps"]
+    out = {}
+    rnd = lambda *shape, std=1.0: (torch.randn(*shape, generator=g) * std)
+    lin = lambda n, k: rnd(n, k, std=k ** -0.5)
+    out["embed"] = rnd(cfg["vocab"], D)
+    out["pos"] = rnd(cfg["max_positions"], D, std=0.5)
+    out["final.norm"], out["final.norm.b"] = 1.0 + rnd(D, std=0.2), rnd(D, std=0.1)
+    for i, L in enumerate(cfg["layers"]):
+        p, m = f"l{i}.", L["mixer"]
+        out[p + "norm1"], out[p + "norm1.b"] = 1.0 + rnd(D, std=0.2), rnd(D, std=0.1)
+        out[p + "canon1"] = rnd(D, K, std=0.4)
+        out[p + "rg1"], out[p + "rg1.b"] = lin(D, D), rnd(D, std=0.5)
+        if L["type"] == "rglru":
+            C, nb, taps = m["width"], m["blocks"], m["conv"]
+            n = C // nb
+            out[p + "mix.y"], out[p + "mix.y.b"], out[p + "mix.x"], out[p + "mix.x.b"] = lin(C, D), rnd(C, std=0.3), lin(C, D), rnd(C, std=0.3)
+            out[p + "mix.conv"], out[p + "mix.conv.b"] = rnd(C, taps, std=0.5) + 0.2, rnd(C, std=0.2)
+            out[p + "mix.ra"], out[p + "mix.ra.b"] = rnd(nb, n, n, std=n ** -0.5), rnd(nb, n, std=0.5)
+            out[p + "mix.ri"], out[p + "mix.ri.b"] = rnd(nb, n, n, std=n ** -0.5), rnd(nb, n, std=0.5)
+            out[p + "mix.lam"] = torch.rand(C, generator=g) * 6.0 - 5.0
+            out[p + "mix.o"] = lin(D, C)
+        elif L["type"] == "lightning":
+            H, dk, dv = m["heads"], m["dim"], m["vdim"]
+            out[p + "mix.q"], out[p + "mix.k"], out[p + "mix.v"], out[p + "mix.g"] = lin(H * dk, D), lin(H * dk, D), lin(H * dv, D), lin(H * dv, D)
+            out[p + "mix.norm"] = 1.0 + rnd(H * dv, std=0.2)
+            out[p + "mix.o"] = lin(D, H * dv)
+        else:
+            l, r = m["left"], m["right"]
+            H, G, dk, dv = l["heads"], l["kv_heads"], l["dim"], l["vdim"]
+            q = "mix.left."
+            out[p + q + "q"], out[p + q + "k"], out[p + q + "v"], out[p + q + "g"] = lin(H * dk, D) * 2.0, lin(G * dk, D) * 2.0, lin(G * dv, D), lin(H, D)
+            out[p + q + "o"], out[p + q + "out"] = lin(D, H * dv), 1.0 + rnd(D, std=0.2)
+            H, dk, dv = r["heads"], r["dim"], r["vdim"]
+            q = "mix.right."
+            out[p + q + "q"], out[p + q + "k"], out[p + q + "v"], out[p + q + "g"] = lin(H * dk, D), lin(H * dk, D), lin(H * dv, D), lin(H * dv, D)
+            out[p + q + "i"], out[p + q + "i.b"], out[p + q + "f"], out[p + q + "f.b"] = lin(H, D) * 2.0, rnd(H), lin(H, D) * 2.0, rnd(H) + 3.0
+            out[p + q + "norm"], out[p + q + "o"], out[p + q + "out"] = 1.0 + rnd(H * dv, std=0.2), lin(D, H * dv), 1.0 + rnd(D, std=0.2)
+        mlp = L.get("mlp")
+        if mlp:
+            out[p + "norm2"], out[p + "norm2.b"] = 1.0 + rnd(D, std=0.2), rnd(D, std=0.1)
+            out[p + "rg2"], out[p + "rg2.b"] = lin(D, D), rnd(D, std=0.5)
+            if mlp["kind"] == "dense":
+                ff = mlp["ff"]
+                out[p + "mlp.gate"], out[p + "mlp.up"], out[p + "mlp.down"] = lin(ff, D), lin(ff, D), lin(D, ff)
+            else:
+                ff, E = mlp["expert"]["ff"], mlp["router"]["experts"]
+                out[p + "mlp.router"] = lin(E, D) * 2.0
+                for j in range(E):
+                    out[p + f"mlp.e{j}.gate"], out[p + f"mlp.e{j}.up"], out[p + f"mlp.e{j}.down"] = lin(ff, D) * 2.0, lin(ff, D) * 2.0, lin(D, ff)
+    return {k: v.to(torch.bfloat16).to(device) for k, v in out.items()}

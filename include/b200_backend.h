@@ -573,6 +573,8 @@ void moe_down(const void* act, const void* w_down, const int32_t* ids, const int
  *   row_scale[scale_index ? scale_index[r] : r]; a negative index marks a padding row, written as zeros.
  * group_rms_norm_gate: out[t, c] = o[t, c] / rms(o[t, group of c]) * weight[c] * act(gate[t, c]); n columns in `groups` equal runs; weight / gate may
  *   be null; gate_act 0 = sigmoid, 1 = SiLU.
+ * head_gate: out[t, h, :dv] = src[t, h, :dv] * sigmoid(gate[t, h]) (gate f32, row pitch ld_gate); src F32 / BF16 [T, H dv], out F32 / BF16 (a BF16
+ *   source goes to a BF16 out).
  * causal_conv_ex: y[t, c] = act(sum_j taps[c, j] in[t - K + 1 + j, c] + out_bias[c]) (+ in[t, c] when add_input), in = x + in_bias (zeros before a
  *   sequence's start); conv_state f32 [slots, max(K - 1, 1), channels] holds a sequence's last K - 1 inputs and is rolled forward.  act 0 = none,
  *   1 = SiLU; y of out_dtype F32 / BF16 with row pitch ldy.
@@ -580,7 +582,8 @@ void moe_down(const void* act, const void* w_down, const int32_t* ids, const int
  *   32-bit products.
  * gated_linear_scan: per channel c of block c / block_channels: r = sigmoid(gates[t, blk, j]), i = sigmoid(gates[t, blk, n + j]) (gates f32 [T, blocks,
  *   2 n], n = block_channels, j = c mod n); log a = -decay_scale r softplus(lam[c]); S <- a S + sqrt(1 - a^2) i u[t, c]; out[t, c] = S *
- *   gelu_tanh(y_pre[t, c] + y_bias[c]).  state f32 [slots, channels].
+ *   gelu_tanh(y_pre[t, c] + y_bias[c]).  state f32 [slots, channels].  max_rows = the most rows any entry brings: from 16 on, the per-row part runs
+ *   as a pass of its own that overwrites gates and y_pre with its results (both are scratch to the caller), and the scan is two multiply-adds per row.
  * linear_attention: per head, S f32 [dk, dv] (stored [slots, H, dv, dk]): S <- a S + b k v^T, o = S^T q; q, k, v = columns off_q / off_k / off_v of
  *   proj f32 [T, ld] (head-major), through SiLU when act == 1, q also times q_scale.  gating 0: a = decay[h], b = 1.  gating 1: with i = cap
  *   tanh((proj[off_i + h] + i_bias[h]) / cap), f = logsigmoid(cap tanh((proj[off_f + h] + f_bias[h]) / cap)) and the running maximum m (0 at the
@@ -602,14 +605,16 @@ void glu_packed(const float* gate_up, void* out, int64_t rows, int32_t ff, int64
                 int32_t out_dtype, int64_t stream);
 void group_rms_norm_gate(const float* o, int64_t ldo, const float* weight, const float* gate, int64_t ld_gate, void* out, int32_t num_tokens, int32_t n,
                          int32_t groups, float eps, int32_t gate_act, int32_t out_dtype, int64_t stream);
+void head_gate(const void* src, int32_t src_dtype, const float* gate, int64_t ld_gate, void* out, int32_t out_dtype, int32_t num_tokens, int32_t num_heads, int32_t dv,
+               int64_t stream);
 void causal_conv_ex(const float* x, int64_t ldx, const float* in_bias, const float* taps, const float* out_bias, float* conv_state, void* y, int64_t ldy,
                     const int32_t* token_seq, const int32_t* cu_seqlens, const int32_t* seq_slots, const int32_t* seq_start, int32_t num_tokens,
                     int32_t num_seqs, int32_t channels, int32_t num_taps, int32_t act, int32_t add_input, int32_t out_dtype, int64_t stream);
 void block_diag_linear(const float* x, int64_t ldx, const float* weight, const float* bias, float* out, int64_t ldy, int32_t num_tokens, int32_t blocks,
                        int32_t rows_per_block, int32_t cols_per_block, int64_t stream);
-void gated_linear_scan(const float* u, int64_t ldu, const float* gates, int64_t ld_gates, const float* lam, const float* y_pre, int64_t ldy, const float* y_bias,
-                       float* state, void* out, const int32_t* cu_seqlens, const int32_t* seq_slots, const int32_t* seq_start, int32_t num_seqs, int32_t channels,
-                       int32_t block_channels, float decay_scale, int32_t out_dtype, int64_t stream);
+void gated_linear_scan(const float* u, int64_t ldu, float* gates, int64_t ld_gates, const float* lam, float* y_pre, int64_t ldy, const float* y_bias,
+                       float* state, void* out, const int32_t* cu_seqlens, const int32_t* seq_slots, const int32_t* seq_start, int32_t num_tokens, int32_t num_seqs,
+                       int32_t max_rows, int32_t channels, int32_t block_channels, float decay_scale, int32_t out_dtype, int64_t stream);
 void linear_attention(const float* proj, int64_t ld, int32_t off_q, int32_t off_k, int32_t off_v, int32_t off_i, int32_t off_f, const float* decay,
                       const float* i_bias, const float* f_bias, float gate_cap, float q_scale, int32_t act, int32_t gating, float* state, float* normaliser,
                       float* maximum, float* out, const int32_t* cu_seqlens, const int32_t* seq_slots, const int32_t* seq_start, int32_t num_seqs,

@@ -203,3 +203,13 @@ def forward(cfg: dict, weights: Dict[str, torch.Tensor], tokens, trace: Optional
         if trace is not None:
             trace.append(x.clone())
     return layer_norm(x, w["final.norm"], w["final.norm.b"], eps) @ w["embed"].T
+
+
+def greedy(cfg: dict, weights: Dict[str, torch.Tensor], prompt, n: int) -> List[int]:
+    """n tokens of greedy continuation (the whole sequence is run again for every token)."""
+    ids, out = list(prompt), []
+    for _ in range(n):
+        t = int(torch.argmax(forward(cfg, weights, ids)[-1]))
+        out.append(t)
+        ids.append(t)
+    return out

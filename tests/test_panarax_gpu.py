@@ -1,0 +1,665 @@
+"""Panarax on the GPU against the plain float64 restatement in oracle/panarax.py: every mechanism alone (with inputs made so that a lost
+state, a far key or a gate left out shows), then whole models through the runner (portions, decode, batches, reused blocks and slots) and
+greedy generation through LLMEngine.  Configurations are small and made here; sizes that one model might happen to make equal (heads ==
+kv_heads, dim == vdim, taps, one expert per token, blocks) differ between the cases."""
+import json
+import math
+import os
+import subprocess
+import sys
+
+import numpy as np
+import pytest
+import torch
+
+import candle_vllm_b200 as pkg
+from candle_vllm_b200 import mixers as M, seq_ops as ops, synthetic as S
+from candle_vllm_b200.engine import LLMEngine, ModelRunner
+from candle_vllm_b200.inputs import prepare_step
+from candle_vllm_b200.panarax import PanaraxConfig, PanaraxModel
+from oracle import panarax as P
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+F64 = torch.float64
+BF = torch.bfloat16
+
+
+def dev(t, dt=torch.float32):
+    return t.to(dt).to(DEV).contiguous()
+
+
+def bf_round(t):
+    return t.to(BF).to(torch.float32)
+
+
+def close(got, want, tol, what=""):
+    got, want = got.detach().cpu().to(F64), want.detach().cpu().to(F64)
+    assert got.shape == want.shape, f"{what}: shape {tuple(got.shape)} vs {tuple(want.shape)}"
+    err = float((got - want).abs().max()) / max(float(want.abs().max()), 1e-30)
+    assert err < tol, f"{what}: max-err/max = {err:.3e} (tolerance {tol})"
+
+
+def portions(total, sizes):
+    out, at, i = [], 0, 0
+    while at < total:
+        n = min(sizes[i % len(sizes)], total - at)
+        out.append((at, n)); at += n; i += 1
+    return out
+
+
+def step(entries, block_size=64):
+    """entries: (start, rows, slot) -> StepBatch without a paged cache behind it"""
+    rows = [dict(tokens=[0] * n, start=s, block_table=list(range(-(-(s + n) // block_size))), state_slot=slot, want=()) for s, n, slot in entries]
+    return ops.StepBatch.from_host(prepare_step(rows, block_size), DEV)
+
+
+def dirty(shape, slots=3):
+    """state tensors as a used pool leaves them: full of another sequence's numbers"""
+    return (torch.randn((slots + 1,) + tuple(shape), generator=torch.Generator().manual_seed(5)) * 7.0).to(DEV)
+
+
+def feed(run, T, sizes, slot=1):
+    """run(batch, lo, hi) over the portions of one sequence in `slot`"""
+    return torch.cat([run(step([(at, n, slot)]), at, at + n) for at, n in portions(T, sizes)])
+
+
+SIZES = [[1000], [1], [2], [3, 1, 2, 17], [16, 1, 15, 33, 2]]
+
+
+# ----------------------------------------------------------------------------------------------------------------------
+# row-wise pieces
+# ----------------------------------------------------------------------------------------------------------------------
+def test_embedding_with_learned_positions():
+    g = torch.Generator().manual_seed(0)
+    tab, pos = torch.randn(50, 33, generator=g).to(BF), torch.randn(20, 33, generator=g).to(BF)
+    b = step([(17, 3, 0), (0, 2, 1)])
+    ids = torch.tensor([3, 49, 0, 3, 7], dtype=torch.int32)
+    b.tokens = ids.to(DEV)
+    want = tab.to(F64)[ids.long()] + pos.to(F64)[torch.tensor([17, 18, 19, 0, 1])]
+    close(ops.embedding_positional(tab.to(DEV), pos.to(DEV), b), want, 1e-6, "bf16 tables")
+    close(ops.embedding_positional(dev(tab), dev(pos), b), want, 1e-6, "f32 tables")
+    with pytest.raises(pkg.BackendError):
+        ops.embedding_positional(tab.to(DEV), pos.to(DEV), step([(18, 3, 0)]))          # position 20 is outside the table
+
+
+@pytest.mark.parametrize("n", [5, 96, 321, 1030])
+def test_layer_norm(n):
+    g = torch.Generator().manual_seed(n)
+    x, w, b = torch.randn(7, n, generator=g) * 3 + 1.5, 1 + torch.randn(n, generator=g) * 0.3, torch.randn(n, generator=g)
+    want = P.layer_norm(x.to(F64), w.to(F64), b.to(F64), 1e-5)
+    close(ops.layer_norm(dev(x), dev(w), dev(b), 1e-5, torch.float32), want, 2e-6, "weight and bias")
+    close(ops.layer_norm(dev(x), dev(w), None, 1e-5, torch.float32), want - b.to(F64), 2e-6, "no bias")
+    o16, o32 = ops.layer_norm(dev(x), dev(w), dev(b), 1e-5, BF, also_f32=True)
+    assert o16.dtype == BF and o32.dtype == torch.float32
+    close(o16, want, 6e-3, "bf16 copy"); close(o32, want, 2e-6, "f32 copy")
+    idx = torch.tensor([6, 0, 3], dtype=torch.int32)
+    close(ops.layer_norm(dev(x), dev(w), dev(b), 1e-5, torch.float32, row_index=idx.to(DEV)), want[idx.long()], 2e-6, "gathered rows")
+    # a large common offset must not leak into the variance
+    close(ops.layer_norm(dev(x + 300.0), dev(w), dev(b), 1e-5, torch.float32), P.layer_norm((x + 300.0).to(F64), w.to(F64), b.to(F64), 1e-5), 2e-4, "offset rows")
+
+
+def test_gated_residual_and_gated_units():
+    g = torch.Generator().manual_seed(1)
+    x, y, z, b = (torch.randn(9, 37, generator=g) for _ in range(3)), None, None, None
+    x, y, z = x
+    b = torch.randn(37, generator=g)
+    wide = torch.randn(9, 37 + 11, generator=g)
+    xd = dev(x)
+    ops.gated_residual_add(xd, dev(y), dev(wide)[:, 11:], dev(b))
+    close(xd, x.to(F64) + torch.sigmoid(wide[:, 11:].to(F64) + b.to(F64)) * y.to(F64), 2e-6, "gated residual (strided gate)")
+    xd = dev(x)
+    ops.gated_residual_add(xd, dev(y), None, None)
+    close(xd, (x + y).to(F64), 1e-6, "plain residual")
+    gu = torch.randn(9, 2 * 37, generator=g) * 3
+    a, u = gu[:, :37].to(F64), gu[:, 37:].to(F64)
+    close(ops.glu_packed(dev(gu), "silu", torch.float32), P.silu(a) * u, 2e-6, "silu")
+    close(ops.glu_packed(dev(gu), "gelu_tanh", torch.float32), P.gelu_tanh(a) * u, 2e-6, "gelu")
+    lim = 1.3
+    clamped = lambda a, u: torch.clamp(a, max=lim) * torch.sigmoid(1.702 * torch.clamp(a, max=lim)) * (torch.clamp(u, -lim, lim) + 1.0)
+    close(ops.glu_packed(dev(gu), "clamped", torch.float32, lim), clamped(a, u), 2e-6, "clamped")
+    # a factor per row, looked up through an index with padding rows
+    sc = torch.rand(5, generator=g) + 0.5
+    idx = torch.tensor([4, -1, 0, 2, 2, 1, -1, 3, 0], dtype=torch.int32)
+    s = sc.to(F64)[idx.clamp(min=0).long()].unsqueeze(1)
+    want = clamped(a * s, u * s) * (idx >= 0).unsqueeze(1)
+    close(ops.glu_packed(dev(gu), "clamped", torch.float32, lim, row_scale=dev(sc), scale_index=idx.to(DEV)), want, 2e-6, "clamped, scaled rows")
+
+
+@pytest.mark.parametrize("groups,gate_act", [(1, "sigmoid"), (3, "sigmoid"), (6, "silu")])
+def test_group_norm_with_gate(groups, gate_act):
+    g = torch.Generator().manual_seed(2)
+    n = 6 * 23
+    o, w, z = torch.randn(5, n, generator=g) * 4, 1 + torch.randn(n, generator=g) * 0.2, torch.randn(5, n + 3, generator=g)
+    gate = torch.sigmoid(z[:, 3:].to(F64)) if gate_act == "sigmoid" else P.silu(z[:, 3:].to(F64))
+    want = P.rms(o.to(F64).view(5, groups, -1), 1e-6).reshape(5, n) * w.to(F64) * gate
+    close(ops.group_rms_norm_gate(dev(o), dev(w), dev(z)[:, 3:], groups, 1e-6, torch.float32, gate_act), want, 3e-6, "gated group norm")
+    close(ops.group_rms_norm_gate(dev(o), None, None, groups, 1e-6, torch.float32), P.rms(o.to(F64).view(5, groups, -1), 1e-6).reshape(5, n), 3e-6, "bare")
+
+
+# ----------------------------------------------------------------------------------------------------------------------
+# short convolutions and the gated recurrence
+# ----------------------------------------------------------------------------------------------------------------------
+@pytest.mark.parametrize("taps,sizes", [(4, [50]), (4, [1]), (3, [2, 1, 5]), (2, [3, 2]), (5, [2, 7, 1, 1, 11]), (1, [4, 1])])
+@pytest.mark.parametrize("form", ["plain", "added", "biased"])
+def test_short_convolution_carries_its_inputs(taps, sizes, form):
+    g = torch.Generator().manual_seed(taps)
+    T, Cn = 50, 70
+    x, w = torch.randn(T, Cn + 9, generator=g), torch.randn(Cn, taps, generator=g)
+    ib, ob = torch.randn(Cn, generator=g), torch.randn(Cn, generator=g)
+    xin = x[:, 9:].to(F64)
+    if form == "plain":
+        want, kw = P.short_conv(xin, w.to(F64)), {}
+    elif form == "added":
+        want, kw = xin + P.short_conv(xin, w.to(F64)), dict(add_input=True)
+    else:
+        want, kw = P.silu(P.short_conv(xin + ib.to(F64), w.to(F64)) + ob.to(F64)), dict(in_bias=dev(ib), out_bias=dev(ob), act="silu")
+    state, xd = dirty((max(taps - 1, 1), Cn)), dev(x)
+    got = feed(lambda b, lo, hi: ops.causal_conv(xd[lo:hi, 9:], dev(w), state, b, **kw), T, sizes)
+    close(got, want, 2e-6, f"{form} convolution, {taps} taps, portions {sizes}")
+
+
+@pytest.mark.parametrize("T,nb,m,n", [(3, 4, 10, 5), (8, 1, 7, 33), (9, 3, 64, 32), (150, 5, 24, 12), (70, 2, 130, 65)])
+def test_block_diagonal_product(T, nb, m, n):
+    g = torch.Generator().manual_seed(T)
+    x, w, b = torch.randn(T, nb * n + 4, generator=g), torch.randn(nb, m, n, generator=g), torch.randn(nb * m, generator=g)
+    want = torch.einsum("bji,tbi->tbj", w.to(F64), x[:, 4:].to(F64).view(T, nb, n)).reshape(T, nb * m) + b.to(F64)
+    close(ops.block_diag_linear(dev(x)[:, 4:], dev(w), dev(b)), want, 3e-6, "block-diagonal product")
+
+
+def _recurrence_case(D, Cn, nb, taps, seed, slow=False):
+    g = torch.Generator().manual_seed(seed)
+    cfg = S.panarax_config(D, 11, [S.panarax_rglru_layer(Cn, nb, conv=taps)], max_positions=8)
+    w = {k[7:]: v.float() for k, v in S.panarax_weights(cfg, seed).items() if k.startswith("l0.mix.")}
+    if slow:
+        w["lam"] = torch.full_like(w["lam"], -9.0)             # decays of 1 - 1e-3: the first tokens still count after hundreds
+    return w, g
+
+
+@pytest.mark.parametrize("D,Cn,nb,taps", [(24, 36, 3, 4), (40, 40, 1, 2), (16, 128, 8, 3), (32, 70, 5, 5)])
+@pytest.mark.parametrize("sizes", SIZES)
+def test_gated_linear_recurrence(D, Cn, nb, taps, sizes):
+    w, g = _recurrence_case(D, Cn, nb, taps, Cn)
+    T = 90
+    h = torch.randn(T, D, generator=g)
+    want = P.rglru_mixer(h.to(F64), {k: v.to(F64) for k, v in w.items()}, nb)
+    mix = M.GatedLinearRecurrence({k: v.to(DEV) for k, v in w.items()}, nb, taps, torch.float32)
+    state, hd = tuple(dirty(s) for s in mix.state_shapes()), dev(h)
+    close(feed(lambda b, lo, hi: mix.forward(hd[lo:hi], b, state), T, sizes), want, 2e-5, f"recurrence, portions {sizes}")
+
+
+def test_recurrence_remembers_its_first_token():
+    """with decays near one and a large first input, a good part of the state after 600 tokens is still the first token's: a state that is
+    lost or restarted at a portion's start shows in every later output"""
+    w, g = _recurrence_case(24, 36, 3, 4, 3, slow=True)
+    T = 600
+    h = torch.randn(T, 24, generator=g) * 0.05
+    h[0] *= 4000.0
+    want = P.rglru_mixer(h.to(F64), {k: v.to(F64) for k, v in w.items()}, 3)
+    without = P.rglru_mixer(h[1:].to(F64), {k: v.to(F64) for k, v in w.items()}, 3)
+    assert float((want[-1] - without[-1]).abs().max()) > 0.3 * float(want[-1].abs().max())              # the first token still counts at the end
+    mix = M.GatedLinearRecurrence({k: v.to(DEV) for k, v in w.items()}, 3, 4, torch.float32)
+    state, hd = tuple(dirty(s) for s in mix.state_shapes()), dev(h)
+    close(feed(lambda b, lo, hi: mix.forward(hd[lo:hi], b, state), T, [200, 1, 1, 57]), want, 5e-5, "slow decays")
+
+
+def test_recurrence_unequal_entries_and_bf16():
+    w, g = _recurrence_case(24, 36, 3, 4, 4)
+    lens = [37, 1, 2, 64]
+    hs = [torch.randn(n, 24, generator=g) for n in lens]
+    wants = [P.rglru_mixer(h.to(F64), {k: v.to(F64) for k, v in w.items()}, 3) for h in hs]
+    mix = M.GatedLinearRecurrence({k: v.to(DEV) for k, v in w.items()}, 3, 4, torch.float32)
+    state = tuple(dirty(s, slots=4) for s in mix.state_shapes())
+    # first step: the first parts of all four, second step: the rest of those that have one, beside each other in another order
+    cut = [20, 1, 1, 30]
+    a = mix.forward(dev(torch.cat([h[:c] for h, c in zip(hs, cut)])), step([(0, c, i) for i, c in enumerate(cut)]), state)
+    rest = [(i, lens[i] - cut[i]) for i in (3, 0, 2) if lens[i] > cut[i]]
+    b = mix.forward(dev(torch.cat([hs[i][cut[i]:] for i, _ in rest])), step([(cut[i], n, i) for i, n in rest]), state)
+    at_a, at_b = np.cumsum([0] + cut), np.cumsum([0] + [n for _, n in rest])
+    for i in range(4):
+        got = a[at_a[i]:at_a[i + 1]]
+        for j, (k, n) in enumerate(rest):
+            if k == i:
+                got = torch.cat([got, b[at_b[j]:at_b[j + 1]]])
+        close(got, wants[i], 2e-5, f"entry {i} of a batch")
+    mix16 = M.GatedLinearRecurrence({k: v.to(DEV) for k, v in w.items()}, 3, 4, BF)
+    state = tuple(dirty(s) for s in mix16.state_shapes())
+    wb = {k: (bf_round(v) if v.dim() > 1 and k not in ("conv", "ra", "ri") else v).to(F64) for k, v in w.items()}
+    close(mix16.forward(dev(hs[0], BF), step([(0, 37, 0)]), state), P.rglru_mixer(bf_round(hs[0]).to(F64), wb, 3), 2e-2, "bf16 products")
+
+
+# ----------------------------------------------------------------------------------------------------------------------
+# linear attention: fixed decay, exponential gating
+# ----------------------------------------------------------------------------------------------------------------------
+def _lightning_weights(D, H, dk, dv, seed, decay=None):
+    cfg = S.panarax_config(D, 11, [S.panarax_lightning_layer(H, dk, dv, decay=decay)], max_positions=8)
+    return cfg["layers"][0]["mixer"]["decay"], {k[7:]: v.float() for k, v in S.panarax_weights(cfg, seed).items() if k.startswith("l0.mix.")}
+
+
+@pytest.mark.parametrize("H,dk,dv", [(3, 12, 20), (2, 64, 64), (2, 100, 40), (1, 256, 16), (4, 32, 130), (2, 30, 17)])
+@pytest.mark.parametrize("sizes", SIZES)
+def test_decay_linear_attention(H, dk, dv, sizes):
+    D, T = 24, 70
+    decay, w = _lightning_weights(D, H, dk, dv, dk + dv)
+    h = torch.randn(T, D, generator=torch.Generator().manual_seed(dk))
+    want = P.lightning_mixer(h.to(F64), {k: v.to(F64) for k, v in w.items()}, H, dk, dv, decay, 1e-6)
+    mix = M.DecayLinearAttention({k: v.to(DEV) for k, v in w.items()}, H, dk, dv, decay, 1e-6, torch.float32)
+    state, hd = tuple(dirty(s) for s in mix.state_shapes()), dev(h)
+    close(feed(lambda b, lo, hi: mix.forward(hd[lo:hi], b, state), T, sizes), want, 2e-5, f"fixed decay, portions {sizes}")
+
+
+def test_decay_attention_keeps_a_far_key():
+    """one head barely decays; one key far back is made large: what the last tokens return is mostly that key's value, in prompts and in decoding"""
+    D, H, dk, dv, T = 24, 2, 16, 24, 500
+    decay, w = _lightning_weights(D, H, dk, dv, 1, decay=[0.5, 0.9995])
+    g = torch.Generator().manual_seed(3)
+    h = torch.randn(T, D, generator=g) * 0.3
+    h[7] *= 40.0
+    f = lambda hh: P.lightning_mixer(hh.to(F64), {k: v.to(F64) for k, v in w.items()}, H, dk, dv, decay, 1e-6)
+    want = f(h)
+    assert float((want[-1] - f(h[8:])[-1]).abs().max()) > 0.2 * float(want[-1].abs().max())          # the far key matters at the end
+    mix = M.DecayLinearAttention({k: v.to(DEV) for k, v in w.items()}, H, dk, dv, decay, 1e-6, torch.float32)
+    for sizes in ([500], [470] + [1] * 30, [64, 64, 3, 200, 1]):
+        state, hd = tuple(dirty(s) for s in mix.state_shapes()), dev(h)
+        close(feed(lambda b, lo, hi: mix.forward(hd[lo:hi], b, state), T, sizes), want, 5e-5, f"far key, portions {sizes[:3]}")
+
+
+def _memory_weights(D, H, dk, dv, seed, cap=12.0):
+    cfg = S.panarax_config(D, 11, [S.panarax_parallel_layer(2, 1, 8, 8, H, dk, dv, gate_cap=cap)], max_positions=8)
+    return {k[13:]: v.float() for k, v in S.panarax_weights(cfg, seed).items() if k.startswith("l0.mix.right.") and k != "l0.mix.right.out"}
+
+
+@pytest.mark.parametrize("H,dk,dv", [(3, 10, 18), (2, 64, 64), (2, 100, 40), (1, 256, 16), (4, 32, 130), (2, 30, 17)])
+@pytest.mark.parametrize("sizes", SIZES)
+def test_matrix_memory(H, dk, dv, sizes):
+    D, T = 24, 70
+    w = _memory_weights(D, H, dk, dv, dk + dv)
+    h = torch.randn(T, D, generator=torch.Generator().manual_seed(dv))
+    want = P.matrix_memory(h.to(F64), {k: v.to(F64) for k, v in w.items()}, H, dk, dv, 12.0, 1e-6)
+    mix = M.MatrixMemoryMixer({k: v.to(DEV) for k, v in w.items()}, H, dk, dv, 12.0, 1e-6, torch.float32)
+    state, hd = tuple(dirty(s) for s in mix.state_shapes()), dev(h)
+    close(feed(lambda b, lo, hi: mix.forward(hd[lo:hi], b, state), T, sizes), want, 5e-5, f"matrix memory, portions {sizes}")
+
+
+@pytest.mark.parametrize("case", ["capped", "closed", "open"])
+def test_matrix_memory_gates(case):
+    """gate pre-activations far beyond the cap (the tanh must hold them), input gates so low that the running maximum stays at its start of
+    zero (a maximum that started lower would divide by something else), and forget gates that keep everything"""
+    D, H, dk, dv, T, cap = 24, 2, 16, 24, 130, 5.0
+    w = _memory_weights(D, H, dk, dv, 8, cap)
+    if case == "capped":
+        w["i"], w["f"] = w["i"] * 30.0, w["f"] * 30.0
+    elif case == "closed":
+        w["i"], w["i.b"], w["f.b"] = w["i"] * 0.1, torch.full_like(w["i.b"], -4.0), torch.full_like(w["f.b"], 6.0)
+    else:
+        w["f"], w["f.b"] = w["f"] * 0.0, torch.full_like(w["f.b"], 40.0)
+    h = torch.randn(T, D, generator=torch.Generator().manual_seed(2))
+    want = P.matrix_memory(h.to(F64), {k: v.to(F64) for k, v in w.items()}, H, dk, dv, cap, 1e-6)
+    mix = M.MatrixMemoryMixer({k: v.to(DEV) for k, v in w.items()}, H, dk, dv, cap, 1e-6, torch.float32)
+    for sizes in ([130], [1], [17, 2, 1]):
+        state, hd = tuple(dirty(s) for s in mix.state_shapes()), dev(h)
+        close(feed(lambda b, lo, hi: mix.forward(hd[lo:hi], b, state), T, sizes), want, 1e-4, f"{case} gates, portions {sizes}")
+
+
+def test_linear_attention_unequal_entries():
+    D, H, dk, dv = 24, 3, 20, 36
+    w = _memory_weights(D, H, dk, dv, 5)
+    g = torch.Generator().manual_seed(6)
+    lens = [33, 1, 2, 50]
+    hs = [torch.randn(n, D, generator=g) for n in lens]
+    wants = [P.matrix_memory(h.to(F64), {k: v.to(F64) for k, v in w.items()}, H, dk, dv, 12.0, 1e-6) for h in hs]
+    mix = M.MatrixMemoryMixer({k: v.to(DEV) for k, v in w.items()}, H, dk, dv, 12.0, 1e-6, torch.float32)
+    state = tuple(dirty(s, slots=4) for s in mix.state_shapes())
+    cut = [16, 1, 1, 17]
+    a = mix.forward(dev(torch.cat([h[:c] for h, c in zip(hs, cut)])), step([(0, c, 3 - i) for i, c in enumerate(cut)]), state)
+    rest = [(i, lens[i] - cut[i]) for i in (2, 3, 0)]
+    b = mix.forward(dev(torch.cat([hs[i][cut[i]:] for i, _ in rest])), step([(cut[i], n, 3 - i) for i, n in rest]), state)
+    at_a, at_b = np.cumsum([0] + cut), np.cumsum([0] + [n for _, n in rest])
+    for i in range(4):
+        got = a[at_a[i]:at_a[i + 1]]
+        for j, (k, n) in enumerate(rest):
+            if k == i:
+                got = torch.cat([got, b[at_b[j]:at_b[j + 1]]])
+        close(got, wants[i], 5e-5, f"entry {i} of a batch")
+
+
+# ----------------------------------------------------------------------------------------------------------------------
+# softmax attention with a query temperature, unit values and head gates
+# ----------------------------------------------------------------------------------------------------------------------
+def _attention_weights(D, H, G, dk, dv, seed):
+    cfg = S.panarax_config(D, 11, [S.panarax_parallel_layer(H, G, dk, dv, 1, 8, 8)], max_positions=8)
+    return {k[12:]: v.float() for k, v in S.panarax_weights(cfg, seed).items() if k.startswith("l0.mix.left.") and k != "l0.mix.left.out"}
+
+
+def _attention_run(w, H, G, dk, dv, scale, q_temp, h, sizes, bs=16, dtype=torch.float32):
+    T = h.shape[0]
+    mix = M.PagedAttentionMixer({k: v.to(DEV) for k, v in w.items()}, H, G, dk, dv, scale, 1e-6, dtype, block_size=bs, max_pos=T, q_temp=q_temp, value_norm=True)
+    nb = -(-T // bs) + 2
+    perm = torch.randperm(nb, generator=torch.Generator().manual_seed(1)).tolist()          # blocks of a used pool, in no order
+    kc = (torch.randn(nb, bs, G, dk) * 9).to(dtype).to(DEV)
+    vc = (torch.randn(nb, bs, G, dv) * 9).to(dtype).to(DEV)
+    hd, out = dev(h, dtype), []
+    for at, n in portions(T, sizes):
+        rows = [dict(tokens=[0] * n, start=at, block_table=perm[:-(-(at + n) // bs)], state_slot=-1, want=())]
+        out.append(mix.forward(hd[at:at + n], ops.StepBatch.from_host(prepare_step(rows, bs), DEV), (kc, vc)))
+    return torch.cat(out)
+
+
+@pytest.mark.parametrize("H,G,dk,dv,every", [(4, 2, 12, 20, 8), (6, 6, 32, 16, 5), (8, 2, 48, 40, 64), (3, 1, 80, 100, 1), (2, 2, 16, 16, 0)])
+@pytest.mark.parametrize("sizes", [[1000], [1], [2], [7, 1, 1, 30], [16, 15, 1, 2]])
+def test_gated_attention(H, G, dk, dv, every, sizes):
+    D, T = 24, 75
+    w = _attention_weights(D, H, G, dk, dv, dk)
+    qt = dict(coef=0.7, every=every) if every else None
+    h = torch.randn(T, D, generator=torch.Generator().manual_seed(dv))
+    want = P.softmax_attention(h.to(F64), {k: v.to(F64) for k, v in w.items()}, H, G, dk, dv, 0.21, 1e-6, qt)
+    close(_attention_run(w, H, G, dk, dv, 0.21, qt, h, sizes), want, 2e-5, f"attention, portions {sizes}")
+
+
+def test_attention_finds_a_far_key_and_the_temperature_steps_at_its_edges():
+    """the key weights are the first head's query weights with the input's entries permuted, and the input at place 5 is the last input permuted
+    back and tripled: key 5 is three times the last query, so what the last row returns is mostly value 5, far back in block 0.  The query
+    temperature with a large coefficient changes how sharp every softmax is at each multiple of `every`, so a position counted one off shows
+    just before and just after such an edge, in a prompt and decoded alone."""
+    D, H, G, dk, dv, T, every = 24, 2, 1, 16, 12, 200, 32
+    w = _attention_weights(D, H, G, dk, dv, 2)
+    g = torch.Generator().manual_seed(4)
+    perm = torch.randperm(D, generator=g)
+    w["k"] = w["q"][:dk][:, perm].clone()
+    h = torch.randn(T, D, generator=g)
+    h[5] = 3.0 * h[T - 1][perm]
+    qt = dict(coef=2.5, every=every)
+    f = lambda hh, q: P.softmax_attention(hh.to(F64), {k: v.to(F64) for k, v in w.items()}, H, G, dk, dv, 0.05, 1e-6, q)
+    want = f(h, qt)
+    off = f(h, dict(coef=2.5, every=every + 1))
+    edges = [30, 31, 32, 62, 63, 64, 191, 192, 199]
+    assert min(float((want[p] - off[p]).abs().max()) for p in (31, 63, 191)) > 5e-3 * float(want.abs().max())
+    without = h.clone()
+    without[5] = 0.0
+    assert float((want[-1] - f(without, qt)[-1]).abs().max()) > 0.5 * float(want[-1].abs().max())
+    for sizes in ([200], [31, 1, 1, 30, 1, 1, 100, 1], [170] + [1] * 30, [16]):
+        got = _attention_run(w, H, G, dk, dv, 0.05, qt, h, sizes)
+        close(got, want, 2e-5, f"portions {sizes[:4]}")
+        close(got[edges], want[edges], 2e-5, "rows beside the temperature's edges and the row that looks far back")
+
+
+def test_attention_bf16_cache():
+    D, H, G, dk, dv, T = 24, 4, 2, 24, 40, 90
+    w = {k: bf_round(v) for k, v in _attention_weights(D, H, G, dk, dv, 3).items()}
+    h = bf_round(torch.randn(T, D, generator=torch.Generator().manual_seed(1)))
+    want = P.softmax_attention(h.to(F64), {k: v.to(F64) for k, v in w.items()}, H, G, dk, dv, 0.2, 1e-6, dict(coef=0.3, every=16))
+    close(_attention_run(w, H, G, dk, dv, 0.2, dict(coef=0.3, every=16), h, [33, 1, 2], dtype=BF), want, 2e-2, "bf16 cache and products")
+
+
+@pytest.mark.parametrize("H,G", [(4, 2), (2, 2), (8, 1)])
+def test_gated_attention_on_the_tensor_core_kernels(H, G):
+    """128-wide heads in bf16 with 64-token blocks: portions run on the tensor-core prefill kernel, steps of single tokens on the split-KV decode
+    kernel; both against the float64 oracle on the bf16-rounded inputs"""
+    D, dk, dv, T = 64, 128, 128, 200
+    w = {k: bf_round(v) for k, v in _attention_weights(D, H, G, dk, dv, 5).items()}
+    h = bf_round(torch.randn(T, D, generator=torch.Generator().manual_seed(7)))
+    qt = dict(coef=0.5, every=48)
+    want = P.softmax_attention(h.to(F64), {k: v.to(F64) for k, v in w.items()}, H, G, dk, dv, 0.03, 1e-6, qt)
+    for sizes in ([200], [130, 3, 1, 1, 40], [150] + [1] * 50):
+        close(_attention_run(w, H, G, dk, dv, 0.03, qt, h, sizes, bs=64, dtype=BF), want, 3e-2, f"tensor-core attention, portions {sizes[:4]}")
+
+
+# ----------------------------------------------------------------------------------------------------------------------
+# sigmoid-routed experts, the parallel pair
+# ----------------------------------------------------------------------------------------------------------------------
+def _expert_weights(D, E, ff, seed):
+    cfg = S.panarax_config(D, 11, [S.panarax_lightning_layer(1, 8, 8, ff=ff, experts=E, top=1)], max_positions=8)
+    return {k[7:]: v.float() for k, v in S.panarax_weights(cfg, seed).items() if k.startswith("l0.mlp.")}
+
+
+@pytest.mark.parametrize("D,E,ff,top,T,dtype", [(24, 5, 12, 1, 9, torch.float32), (40, 7, 20, 3, 50, torch.float32), (24, 2, 10, 2, 4, torch.float32),
+                                                (64, 6, 64, 2, 40, BF), (128, 9, 96, 2, 200, BF), (64, 3, 72, 1, 3, BF), (40, 4, 20, 2, 30, BF)])
+def test_sigmoid_routed_clamped_experts(D, E, ff, top, T, dtype):
+    w = _expert_weights(D, E, ff, E)
+    h = torch.randn(T, D, generator=torch.Generator().manual_seed(T))
+    if dtype == BF:
+        w, h = {k: bf_round(v) for k, v in w.items()}, bf_round(h)
+    lim = 0.8                                             # well inside what the products reach: both clamps act
+    want = P.sigmoid_moe(h.to(F64), {k: v.to(F64) for k, v in w.items()}, E, top, lim)
+    mlp = M.RoutedExperts({k: v.to(DEV) for k, v in w.items()}, E, 0, top, 1.0, dtype, score="sigmoid", normalise=False, weight_input=True, act="clamped", limit=lim)
+    got = mlp.forward(dev(h, dtype), dev(h))
+    close(got, want, 2e-5 if dtype == torch.float32 else 2e-2, f"{E} experts, top {top}, {dtype}")
+    # every score counts as it is: doubling the chosen score doubles what the expert sees, not what it returns
+    s = torch.sigmoid(h.to(F64) @ w["router"].to(F64).T)
+    e0 = int(torch.argmax(s[0]))
+    alone = P.clamped_expert(s[0, e0] * h[0].to(F64), w[f"e{e0}.gate"].to(F64), w[f"e{e0}.up"].to(F64), w[f"e{e0}.down"].to(F64), lim)
+    if top == 1:
+        close(got[0], alone, 2e-5 if dtype == torch.float32 else 2e-2, "the best expert alone")
+
+
+def test_parallel_pair():
+    D, T = 32, 60
+    cfg = S.panarax_config(D, 11, [S.panarax_parallel_layer(4, 2, 12, 20, 3, 10, 18, q_temp=(0.4, 7), gate_cap=9.0, scale=0.3)], max_positions=8)
+    m = cfg["layers"][0]["mixer"]
+    w = {k[7:]: v.float() for k, v in S.panarax_weights(cfg, 1).items() if k.startswith("l0.mix.")}
+    h = torch.randn(T, D, generator=torch.Generator().manual_seed(9))
+    want = P.parallel_mixer(h.to(F64), {k: v.to(F64) for k, v in w.items()}, m, 1e-6)
+    wd = {k: v.to(DEV) for k, v in w.items()}
+    left = M.PagedAttentionMixer({k[5:]: v for k, v in wd.items() if k.startswith("left.") and k != "left.out"}, 4, 2, 12, 20, 0.3, 1e-6, torch.float32, block_size=16,
+                                 max_pos=T, q_temp=m["left"]["q_temp"], value_norm=True)
+    right = M.MatrixMemoryMixer({k[6:]: v for k, v in wd.items() if k.startswith("right.") and k != "right.out"}, 3, 10, 18, 9.0, 1e-6, torch.float32)
+    mix = M.ParallelMixer(left, right, wd["left.out"], wd["right.out"], 1e-6)
+    kc, vc = torch.zeros(5, 16, 2, 12, device=DEV), torch.zeros(5, 16, 2, 20, device=DEV)
+    state, hd, out = tuple(dirty(s) for s in mix.state_shapes()), dev(h), []
+    for at, n in portions(T, [13, 1, 2, 30]):
+        rows = [dict(tokens=[0] * n, start=at, block_table=[4, 2, 0, 1][:-(-(at + n) // 16)], state_slot=1, want=())]
+        out.append(mix.forward(hd[at:at + n], ops.StepBatch.from_host(prepare_step(rows, 16), DEV), (kc, vc), state))
+    close(torch.cat(out), want, 3e-5, "attention and matrix memory side by side")
+
+
+# ----------------------------------------------------------------------------------------------------------------------
+# whole models through the runner
+# ----------------------------------------------------------------------------------------------------------------------
+CONFIGS = {
+    # every mixer and both feed-forwards, nothing equal to anything else
+    "mixed": S.panarax_config(48, 97, [S.panarax_parallel_layer(4, 2, 12, 20, 3, 10, 18, q_temp=(0.3, 16), ff=40),
+                                       S.panarax_rglru_layer(36, 3, conv=4, ff=24, experts=5, top=2, limit=1.5),
+                                       S.panarax_lightning_layer(3, 12, 20, ff=56),
+                                       S.panarax_lightning_layer(2, 24, 8, ff=16, experts=3, top=1, limit=2.0),
+                                       S.panarax_parallel_layer(6, 6, 8, 8, 1, 16, 40, q_temp=None, gate_cap=6.0, scale=0.5)], max_positions=320, taps=3),
+    # another order, another width of the recurrence than the model's, two taps, a layer without feed-forward
+    "recurrent": S.panarax_config(32, 61, [S.panarax_rglru_layer(64, 8, conv=2, ff=48), S.panarax_rglru_layer(24, 1, conv=5),
+                                           S.panarax_parallel_layer(2, 1, 16, 24, 2, 16, 16, q_temp=(1.0, 64), ff=32, experts=4, top=3, limit=1.0)], max_positions=320, taps=2),
+    # sizes the tensor-core products take in bf16 (multiples of 8, 64 and more)
+    "wide": S.panarax_config(128, 211, [S.panarax_lightning_layer(2, 64, 64, ff=128, experts=4, top=2, limit=3.0),
+                                        S.panarax_parallel_layer(4, 2, 64, 32, 2, 32, 64, ff=192),
+                                        S.panarax_rglru_layer(128, 4, ff=64, experts=6, top=1, limit=2.0)], max_positions=320, taps=4),
+}
+# 128-wide attention heads: in bf16 the tensor-core attention kernels serve prompts and decoding
+CONFIGS["heads128"] = S.panarax_config(64, 83, [S.panarax_parallel_layer(2, 1, 128, 128, 2, 32, 32, q_temp=(0.3, 50), scale=0.05, ff=64),
+                                                S.panarax_lightning_layer(2, 128, 128, ff=32, experts=3, top=2, limit=2.5)], max_positions=320, taps=3)
+_CACHE = {}
+TOL = {torch.float32: 2e-4, BF: 8e-2}
+
+
+def model_and_oracle(name, dtype, n_tokens, seed=0):
+    cfg = CONFIGS[name]
+    key = (name, seed)
+    if key not in _CACHE:
+        w = S.panarax_weights(cfg, seed)
+        toks = torch.randint(0, cfg["vocab"], (300,), generator=torch.Generator().manual_seed(seed + 1)).tolist()
+        _CACHE[key] = (w, toks, P.forward(cfg, w, toks))
+    w, toks, ref = _CACHE[key]
+    model = PanaraxModel(PanaraxConfig.from_dict(cfg), w, dtype=dtype, block_size=64, device=DEV)
+    return model, toks[:n_tokens], ref[:n_tokens]
+
+
+def run_schedule(runner, seq_id, toks, sizes):
+    runner.admit(seq_id)
+    out = [runner.execute([dict(seq_id=seq_id, tokens=toks[at:at + n], want=list(range(n)))]) for at, n in portions(len(toks), sizes)]
+    runner.release(seq_id)
+    return torch.cat(out)
+
+
+@pytest.mark.parametrize("name", list(CONFIGS))
+@pytest.mark.parametrize("dtype", [torch.float32, BF])
+def test_whole_prompt_matches_the_oracle(name, dtype):
+    model, toks, ref = model_and_oracle(name, dtype, 200)
+    runner = ModelRunner(model, 4, 1, 64)
+    trace = []
+    runner.admit(0)
+    got = runner.execute([dict(seq_id=0, tokens=toks, want=list(range(200)))], hidden_trace=trace)
+    assert len(trace) == len(CONFIGS[name]["layers"])
+    close(got, ref, TOL[dtype], f"{name} {dtype}")
+    if dtype == torch.float32:
+        oracle_trace = []
+        P.forward(CONFIGS[name], _CACHE[(name, 0)][0], toks, oracle_trace)
+        for i, (a, b) in enumerate(zip(trace, oracle_trace)):
+            close(a, b, 1e-4, f"{name}: stream after layer {i}")
+
+
+@pytest.mark.parametrize("name", list(CONFIGS))
+@pytest.mark.parametrize("sizes", [[1], [2], [3, 2, 7], [64, 1, 1, 5], [39, 1, 41, 2, 63]])
+def test_portions_and_decoding_match_the_whole_prompt(name, sizes):
+    model, toks, ref = model_and_oracle(name, torch.float32, 150)
+    close(run_schedule(ModelRunner(model, 3, 1, 64), 0, toks, sizes), ref, TOL[torch.float32], f"{name} in portions {sizes}")
+
+
+@pytest.mark.parametrize("name", ["wide", "heads128"])
+def test_portions_in_bf16_stay_within_rounding(name):
+    model, toks, ref = model_and_oracle(name, BF, 150)
+    whole = run_schedule(ModelRunner(model, 3, 1, 64), 0, toks, [150])
+    for sizes in ([2], [64, 1, 1, 5], [100] + [1] * 50):
+        got = run_schedule(ModelRunner(model, 3, 1, 64), 0, toks, sizes)
+        close(got, ref, TOL[BF], f"bf16 portions {sizes[:4]} against the oracle")
+        close(got, whole, 4e-2, f"bf16 portions {sizes[:4]} against the whole prompt")
+
+
+@pytest.mark.parametrize("name", ["mixed", "recurrent"])
+def test_unequal_batches_match_each_request_alone(name):
+    """Requests of different lengths advance together, portions of some beside single tokens of others; the pool is smaller than the sum of all
+    requests, so blocks and slots of finished requests go to later ones (slots are handed over dirty)."""
+    cfg = CONFIGS[name]
+    w = S.panarax_weights(cfg, 0)
+    model = PanaraxModel(PanaraxConfig.from_dict(cfg), w, dtype=torch.float32, block_size=64, device=DEV)
+    g = torch.Generator().manual_seed(9)
+    lens = [130, 7, 64, 201, 65, 1, 90]
+    seqs = [torch.randint(0, cfg["vocab"], (n,), generator=g).tolist() for n in lens]
+    refs = [P.forward(cfg, w, s) for s in seqs]
+    runner = ModelRunner(model, 9, 3, 64)
+    plans = [[64, 1, 1, 30, 2, 1], [2, 1], [63, 1], [100, 3, 1, 1, 50, 2], [64, 1], [1], [1, 1, 1, 80, 2]]
+    waiting, live, got = list(range(len(seqs))), {}, {i: [] for i in range(len(seqs))}
+    guard = 0
+    while waiting or live:
+        guard += 1
+        assert guard < 500
+        while waiting and runner.can_admit(lens[waiting[0]], sum(-(-lens[i] // 64) - len(runner.blocks.tables.get(i, ())) for i in live)):
+            i = waiting.pop(0)
+            runner.admit(i)
+            live[i] = [0, 0]
+        entries = []
+        for i, (fed, pi) in live.items():
+            n = min(plans[i][pi] if pi < len(plans[i]) else 1, lens[i] - fed)
+            entries.append(dict(seq_id=i, tokens=seqs[i][fed:fed + n], want=list(range(n))))
+        out = runner.execute(entries)
+        at = 0
+        for e in entries:
+            i, n = e["seq_id"], len(e["tokens"])
+            got[i].append(out[at:at + n]); at += n
+            live[i][0] += n; live[i][1] += 1
+        for i in [i for i, (fed, _) in live.items() if fed == lens[i]]:
+            runner.release(i); del live[i]
+    for i in range(len(seqs)):
+        close(torch.cat(got[i]), refs[i], TOL[torch.float32], f"{name} request {i} in a batch")
+    runner.blocks.check_invariants()
+    assert runner.blocks.num_free_gpu_blocks() == 9 and runner.state.pool.num_free() == 3
+
+
+def test_long_decoding_and_first_tokens():
+    model, toks, ref = model_and_oracle("mixed", torch.float32, 300)
+    runner = ModelRunner(model, 5, 2, 64)
+    runner.admit(0)
+    got = [runner.execute([dict(seq_id=0, tokens=toks[:20], want=list(range(20)))])]
+    for t in range(20, 300):
+        got.append(runner.execute([dict(seq_id=0, tokens=[toks[t]], want=[0])]))
+    close(torch.cat(got), ref, TOL[torch.float32], "280 decoded tokens")
+    runner.release(0)
+    for n in (1, 2, 3):
+        runner.admit(n)
+        close(runner.execute([dict(seq_id=n, tokens=toks[:n], want=list(range(n)))]), ref[:n], TOL[torch.float32], f"first {n} tokens")
+        runner.release(n)
+
+
+def _checkpoint(tmp_path, name, seed):
+    from candle_vllm_b200.safetensors_io import save_file
+    cfg = CONFIGS[name]
+    w = S.panarax_weights(cfg, seed)
+    save_file(w, str(tmp_path / "model.safetensors"))
+    (tmp_path / "config.json").write_text(json.dumps(cfg))
+    return cfg, w
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, BF])
+def test_greedy_generation_through_the_engine(dtype, tmp_path):
+    """checkpoint on disk -> registry -> LLMEngine (scheduler, chunked prefill, sampler) against the oracle's greedy continuation"""
+    cfg, w = _checkpoint(tmp_path, "mixed", 4)
+    g = torch.Generator().manual_seed(2)
+    prompts = [torch.randint(0, cfg["vocab"], (n,), generator=g).tolist() for n in (70, 3, 33, 1, 129)]
+    eng = LLMEngine.from_pretrained(str(tmp_path), dtype=dtype, num_blocks=7, max_num_seqs=2, prefill_chunk=48, max_batch_tokens=64, max_model_len=256)
+    assert isinstance(eng.model, PanaraxModel)
+    outs = eng.generate(prompts, pkg.SamplingParams(max_tokens=6))
+    assert eng.runner.blocks.num_free_gpu_blocks() == 7 and eng.runner.state.pool.num_free() == 2
+    for p, o in zip(prompts, outs):
+        assert len(o) == 6
+        ids = list(p)
+        for t in o:       # a near-tie may flip: every produced token must be within rounding of the oracle's best at its place
+            lg = P.forward(cfg, w, ids)[-1]
+            assert float(lg.max() - lg[t]) < (1e-3 if dtype == torch.float32 else 0.05) * float(lg.abs().max())
+            ids.append(t)
+
+
+def test_graph_replay_of_decode_steps_matches_eager():
+    cfg = CONFIGS["recurrent"]
+    w = S.panarax_weights(cfg, 0)
+    model = PanaraxModel(PanaraxConfig.from_dict(cfg), w, dtype=torch.float32, block_size=64, device=DEV)
+    g = torch.Generator().manual_seed(3)
+    seqs = [torch.randint(0, cfg["vocab"], (n,), generator=g).tolist() for n in (100, 140)]
+    refs = [P.forward(cfg, w, s) for s in seqs]
+    runner = ModelRunner(model, 6, 2, 64, decode_graphs=True)
+    got = [[], []]
+    runner.admit(0); runner.admit(1)
+    out = runner.execute([dict(seq_id=0, tokens=seqs[0][:50], want=list(range(50))), dict(seq_id=1, tokens=seqs[1][:61], want=list(range(61)))])
+    got[0].append(out[:50]); got[1].append(out[50:])
+    fed = [50, 61]
+    while fed[0] < 100 or fed[1] < 140:
+        live = [i for i in (0, 1) if fed[i] < len(seqs[i])]
+        out = runner.execute([dict(seq_id=i, tokens=[seqs[i][fed[i]]], want=[0]) for i in live]).clone()
+        for r, i in enumerate(live):
+            got[i].append(out[r:r + 1]); fed[i] += 1
+    assert 1 in runner._graphs and 2 in runner._graphs
+    for i in (0, 1):
+        close(torch.cat(got[i]), refs[i], TOL[torch.float32], f"graph replay, request {i}")
+
+
+def test_command_line_and_trace_runner(tmp_path):
+    """the two programs a user starts, as child processes on a checkpoint on disk: `generate` against the oracle's greedy continuation,
+    `bin/trace_run` fed steps (a portion of one request beside the first token of another, then single tokens; the first request ends and a
+    third takes its slot) against the oracle's logits"""
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    cfg, w = _checkpoint(tmp_path, "recurrent", 7)
+    env = dict(os.environ, PYTHONPATH=root)
+    r = subprocess.run([sys.executable, "-m", "candle_vllm_b200", "generate", "--model", str(tmp_path), "--dtype", "float32", "--prompt-ids", "5,9,2,40",
+                        "--max-new-tokens", "5", "--num-blocks", "4"], capture_output=True, text=True, env=env, timeout=600)
+    assert r.returncode == 0, r.stderr[-2000:]
+    assert json.loads(r.stdout.strip().splitlines()[-1])["output"] == P.greedy(cfg, w, [5, 9, 2, 40], 5)
+    g = torch.Generator().manual_seed(1)
+    a, b, c = (torch.randint(0, cfg["vocab"], (n,), generator=g).tolist() for n in (70, 5, 9))
+    steps = [dict(step=0, entries=[dict(id="a", tokens=a[:66], want=[0, 63, 64, 65]), dict(id="b", tokens=b[:1], want=[0])], end=[]),
+             dict(step=1, entries=[dict(id="a", tokens=a[66:], want=[3]), dict(id="b", tokens=b[1:3], want=[])], end=["a"]),
+             dict(step=2, entries=[dict(id="c", tokens=c, want=[8]), dict(id="b", tokens=b[3:], want=[0, 1])], end=["b", "c"])]
+    out = tmp_path / "out"
+    r = subprocess.run([os.path.join(root, "bin", "trace_run"), "--model", str(tmp_path), "--dtype", "float32", "--out", str(out), "--max-tokens", "192", "--slots", "2"],
+                       input="\n".join(json.dumps(s) for s in steps) + "\n", capture_output=True, text=True, env=env, timeout=600)
+    assert r.returncode == 0, r.stderr[-2000:]
+    assert [l for l in r.stdout.splitlines() if l.startswith("done")] == ["done 0", "done 1", "done 2"]
+    ra, rb, rc = (P.forward(cfg, w, s) for s in (a, b, c))
+    V = cfg["vocab"]
+    read = lambda n: torch.from_numpy(np.fromfile(out / f"{n}.f32", dtype="<f4").reshape(-1, V).copy())
+    close(read(0), torch.cat([ra[[0, 63, 64, 65]], rb[[0]]]), TOL[torch.float32], "step 0")
+    close(read(1), ra[[69]], TOL[torch.float32], "step 1")
+    close(read(2), torch.cat([rc[[8]], rb[[3, 4]]]), TOL[torch.float32], "step 2")
