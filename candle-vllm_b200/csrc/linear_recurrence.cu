@@ -90,6 +90,34 @@ causal_conv_roll_kernel(const float* __restrict__ x, int64_t ldx, const float* _
     }
 }
 
+// Steps in which every entry brings one row: the convolution and the roll of the state in one kernel (a thread owns its channel's state column)
+template <typename TOut>
+__global__ void __launch_bounds__(128)
+causal_conv_step_kernel(const float* __restrict__ x, int64_t ldx, const float* __restrict__ in_bias, const float* __restrict__ taps,
+                        const float* __restrict__ out_bias, float* __restrict__ conv_state, TOut* __restrict__ y, int64_t ldy,
+                        const int32_t* __restrict__ seq_slots, const int32_t* __restrict__ seq_start, int C, int K, int act, int add_input) {
+    pdl_wait();
+    pdl_trigger();
+    const int c = blockIdx.x * 128 + threadIdx.x;
+    const int b = blockIdx.y;
+    if (c >= C) return;
+    const bool fresh = seq_start[b] == 0;
+    float* st = conv_state + (int64_t)seq_slots[b] * (K > 1 ? K - 1 : 1) * C;
+    const float cur = x[(int64_t)b * ldx + c] + (in_bias ? in_bias[c] : 0.f);
+    float acc = 0.f;
+    for (int j = 0; j < K - 1; ++j) {             // oldest input first; row j moves to row j - 1
+        const float v = fresh ? 0.f : st[(int64_t)j * C + c];
+        acc = fmaf(taps[(int64_t)c * K + j], v, acc);
+        if (j > 0) st[(int64_t)(j - 1) * C + c] = v;
+    }
+    if (K > 1) st[(int64_t)(K - 2) * C + c] = cur;
+    acc = fmaf(taps[(int64_t)c * K + K - 1], cur, acc);
+    if (out_bias) acc += out_bias[c];
+    if (act == 1) acc = silu_f(acc);
+    if (add_input) acc += cur;
+    y[(int64_t)b * ldy + c] = from_f32<TOut>(acc);
+}
+
 // ---- block-diagonal f32 product ---------------------------------------------------------------------------------------------------
 constexpr int kBM = 64, kBN = 64, kBK = 16;
 
@@ -409,7 +437,13 @@ linear_attention_kernel(const LinAttnArgs A) {
         }
         __syncthreads();
         if (tb + kTile < t1) fetch(tb + kTile);
-        for (int tt = 0; tt < nt; ++tt) {
+        // the tile's tokens one after the other; every token leaves a partial sum per lane, and the butterflies that join the eight parts run
+        // afterwards for all tokens together (sixteen independent chains instead of one per token on the serial path)
+        float osum[kTile], nsum[kTile];
+#pragma unroll
+        for (int tt = 0; tt < kTile; ++tt) {
+            osum[tt] = 0.f; nsum[tt] = 0.f;
+            if (tt >= nt) continue;
             const float a = kExp ? sa[tt] : fixed_a;
             const float bv = (kExp ? sb[tt] : 1.0f) * sv[tt * 16 + colb];
             const float bn = kExp ? sb[tt] : 0.f;
@@ -428,14 +462,23 @@ linear_attention_kernel(const LinAttnArgs A) {
                     if (kExp) { nv[r] = fmaf(a, nv[r], ka[j] * bn); nq[j & 1] = fmaf(nv[r], qa[j], nq[j & 1]); }
                 }
             }
-            float o = acc[0] + acc[1], nqs = nq[0] + nq[1];
+            osum[tt] = acc[0] + acc[1];
+            if (kExp) nsum[tt] = nq[0] + nq[1];
+        }
 #pragma unroll
-            for (int sh = 4; sh < 32; sh <<= 1) {
-                o += __shfl_xor_sync(0xffffffffu, o, sh);
-                if (kExp) nqs += __shfl_xor_sync(0xffffffffu, nqs, sh);
+        for (int sh = 4; sh < 32; sh <<= 1) {
+#pragma unroll
+            for (int tt = 0; tt < kTile; ++tt) {
+                osum[tt] += __shfl_xor_sync(0xffffffffu, osum[tt], sh);
+                if (kExp) nsum[tt] += __shfl_xor_sync(0xffffffffu, nsum[tt], sh);
             }
-            if (part == 0 && col_ok) {
-                if (kExp) o = o / (fmaxf(fabsf(nqs), se[tt]) + 1e-6f);
+        }
+        if (part == 0 && col_ok) {
+#pragma unroll
+            for (int tt = 0; tt < kTile; ++tt) {
+                if (tt >= nt) continue;
+                float o = osum[tt];
+                if (kExp) o = o / (fmaxf(fabsf(nsum[tt]), se[tt]) + 1e-6f);
                 A.out[(int64_t)(tb + tt) * H * dv + h * dv + col] = o;
             }
         }
@@ -465,19 +508,123 @@ linear_attention_kernel(const LinAttnArgs A) {
     }
 }
 
+// Steps in which every entry brings one token (row b belongs to entry b): nothing is staged and no thread waits for another -- a lane reads its
+// own rows of q and k, its column's value and (exponential gating) the two gate values straight from the projection, takes one pass over its
+// rows of the state and writes them back.  Same lane layout and state layout as the kernel above.
 template <int kR, bool kExp>
-void launch_linear_attention(const LinAttnArgs& A, int num_seqs, cudaStream_t st) {
+__global__ void __launch_bounds__(128)
+linear_attention_step_kernel(const LinAttnArgs A) {
+    pdl_wait();
+    pdl_trigger();
+    const int h = blockIdx.y, b = blockIdx.z;
+    const int H = A.H, dk = A.dk, dv = A.dv;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int part = lane >> 2, cl = lane & 3;
+    const int col = blockIdx.x * 16 + warp * 4 + cl;
+    const bool col_ok = col < dv;
+    const bool fresh = A.seq_start[b] == 0;
+    const int64_t slot = A.seq_slots[b];
+    const bool vec = (dk & 3) == 0;
+    float* Sp = A.S + ((slot * H + h) * dv + (col_ok ? col : 0)) * (int64_t)dk + part * kR;
+    const int64_t own = (slot * H + h) * (int64_t)gridDim.x + blockIdx.x;
+    float* np = kExp ? A.nrm + own * dk + part * kR : nullptr;
+    const float* row = A.proj + (int64_t)b * A.ld;
+    float S[kR], nv[kR], q[kR], k[kR];
+#pragma unroll
+    for (int r = 0; r < kR; ++r) {
+        const int g = part * kR + r;
+        const bool ok = g < dk;
+        S[r] = 0.f; nv[r] = 0.f;
+        q[r] = ok ? row[A.off_q + h * dk + g] : 0.f;
+        k[r] = ok ? row[A.off_k + h * dk + g] : 0.f;
+    }
+    float v = col_ok ? row[A.off_v + h * dv + col] : 0.f;
+    float zi = 0.f, zf = 0.f, m_prev = 0.f;
+    if (kExp) {
+        zi = row[A.off_i + h] + (A.i_bias ? A.i_bias[h] : 0.f);
+        zf = row[A.off_f + h] + (A.f_bias ? A.f_bias[h] : 0.f);
+        if (!fresh) m_prev = A.mx[own];
+    }
+    if (!fresh) {
+        if (vec) {
+#pragma unroll
+            for (int r4 = 0; r4 < kR / 4; ++r4) {
+                if (part * kR + r4 * 4 >= dk) continue;
+                if (col_ok) { const float4 t = reinterpret_cast<const float4*>(Sp)[r4]; S[r4 * 4] = t.x; S[r4 * 4 + 1] = t.y; S[r4 * 4 + 2] = t.z; S[r4 * 4 + 3] = t.w; }
+                if (kExp) { const float4 t = reinterpret_cast<const float4*>(np)[r4]; nv[r4 * 4] = t.x; nv[r4 * 4 + 1] = t.y; nv[r4 * 4 + 2] = t.z; nv[r4 * 4 + 3] = t.w; }
+            }
+        } else {
+#pragma unroll
+            for (int r = 0; r < kR; ++r) {
+                const bool ok = part * kR + r < dk;
+                if (col_ok && ok) S[r] = Sp[r];
+                if (kExp && ok) nv[r] = np[r];
+            }
+        }
+    }
+    float a = kExp ? 0.f : A.decay[h], bw = 1.0f, em = 0.f, m_new = 0.f;
+    if (kExp) {
+        const float gi = A.cap * tanhf(zi / A.cap), gf = log_sigmoid_f(A.cap * tanhf(zf / A.cap));
+        m_new = fmaxf(gf + m_prev, gi);
+        a = expf(gf + m_prev - m_new); bw = expf(gi - m_new); em = expf(-m_new);
+    }
+    if (A.act == 1) v = silu_f(v);
+    const float bv = bw * v;
+    float acc[2] = {0.f, 0.f}, nq[2] = {0.f, 0.f};
+#pragma unroll
+    for (int r = 0; r < kR; ++r) {
+        float qv = q[r], kv = k[r];
+        if (A.act == 1) { qv = silu_f(qv); kv = silu_f(kv); }
+        qv *= A.q_scale;
+        S[r] = fmaf(a, S[r], kv * bv);
+        acc[r & 1] = fmaf(S[r], qv, acc[r & 1]);
+        if (kExp) { nv[r] = fmaf(a, nv[r], kv * bw); nq[r & 1] = fmaf(nv[r], qv, nq[r & 1]); }
+    }
+    float o = acc[0] + acc[1], nqs = nq[0] + nq[1];
+#pragma unroll
+    for (int sh = 4; sh < 32; sh <<= 1) {
+        o += __shfl_xor_sync(0xffffffffu, o, sh);
+        if (kExp) nqs += __shfl_xor_sync(0xffffffffu, nqs, sh);
+    }
+    if (part == 0 && col_ok) {
+        if (kExp) o = o / (fmaxf(fabsf(nqs), em) + 1e-6f);
+        A.out[(int64_t)b * H * dv + h * dv + col] = o;
+    }
+    if (vec) {
+#pragma unroll
+        for (int r4 = 0; r4 < kR / 4; ++r4) {
+            if (part * kR + r4 * 4 >= dk) continue;
+            if (col_ok) reinterpret_cast<float4*>(Sp)[r4] = make_float4(S[r4 * 4], S[r4 * 4 + 1], S[r4 * 4 + 2], S[r4 * 4 + 3]);
+            if (kExp && warp == 0 && cl == 0) reinterpret_cast<float4*>(np)[r4] = make_float4(nv[r4 * 4], nv[r4 * 4 + 1], nv[r4 * 4 + 2], nv[r4 * 4 + 3]);
+        }
+    } else {
+#pragma unroll
+        for (int r = 0; r < kR; ++r) {
+            const bool ok = part * kR + r < dk;
+            if (col_ok && ok) Sp[r] = S[r];
+            if (kExp && ok && warp == 0 && cl == 0) np[r] = nv[r];
+        }
+    }
+    if (kExp && threadIdx.x == 0) A.mx[own] = m_new;
+}
+
+template <int kR, bool kExp>
+void launch_linear_attention(const LinAttnArgs& A, int num_seqs, bool single_rows, cudaStream_t st) {
+    if (single_rows) {
+        launch_pdl(linear_attention_step_kernel<kR, kExp>, dim3(ceil_div(A.dv, 16), A.H, num_seqs), dim3(128), 0, st, A);
+        return;
+    }
     const int smem = (2 * kTile * 8 * kR + kTile * 16 + 6 * kTile + 1) * (int)sizeof(float);
     ensure_dynamic_smem(reinterpret_cast<const void*>(linear_attention_kernel<kR, kExp>), smem);
     launch_pdl(linear_attention_kernel<kR, kExp>, dim3(ceil_div(A.dv, 16), A.H, num_seqs), dim3(128), (size_t)smem, st, A);
 }
 
 template <bool kExp>
-bool dispatch_linear_attention(const LinAttnArgs& A, int num_seqs, cudaStream_t st) {
-    if (A.dk <= 32) launch_linear_attention<4, kExp>(A, num_seqs, st);
-    else if (A.dk <= 64) launch_linear_attention<8, kExp>(A, num_seqs, st);
-    else if (A.dk <= 128) launch_linear_attention<16, kExp>(A, num_seqs, st);
-    else if (A.dk <= 256) launch_linear_attention<32, kExp>(A, num_seqs, st);
+bool dispatch_linear_attention(const LinAttnArgs& A, int num_seqs, bool single_rows, cudaStream_t st) {
+    if (A.dk <= 32) launch_linear_attention<4, kExp>(A, num_seqs, single_rows, st);
+    else if (A.dk <= 64) launch_linear_attention<8, kExp>(A, num_seqs, single_rows, st);
+    else if (A.dk <= 128) launch_linear_attention<16, kExp>(A, num_seqs, single_rows, st);
+    else if (A.dk <= 256) launch_linear_attention<32, kExp>(A, num_seqs, single_rows, st);
     else return false;
     return true;
 }
@@ -491,12 +638,25 @@ extern "C" {
 
 void causal_conv_ex(const float* x, int64_t ldx, const float* in_bias, const float* taps, const float* out_bias, float* conv_state, void* y, int64_t ldy,
                     const int32_t* token_seq, const int32_t* cu_seqlens, const int32_t* seq_slots, const int32_t* seq_start, int32_t num_tokens,
-                    int32_t num_seqs, int32_t channels, int32_t num_taps, int32_t act, int32_t add_input, int32_t out_dtype, int64_t stream) {
+                    int32_t num_seqs, int32_t single_rows, int32_t channels, int32_t num_taps, int32_t act, int32_t add_input, int32_t out_dtype, int64_t stream) {
     if (num_tokens == 0 || num_seqs == 0) return;
     B200_REQUIRE(x && taps && conv_state && y && token_seq && cu_seqlens && seq_slots && seq_start && channels > 0 && num_taps >= 1 && ldx >= channels &&
                  ldy >= channels && num_tokens <= 65535 && num_seqs <= 65535 && (act == 0 || act == 1), kErrBadArg, "causal_conv_ex: bad arguments");
     cudaStream_t st = as_stream(stream);
     const dim3 grid(ceil_div(channels, 128), num_tokens);
+    if (single_rows) {
+        B200_REQUIRE(num_tokens == num_seqs, kErrBadArg, "causal_conv_ex: the single-row kernel takes one row per entry");
+        if (out_dtype == B200_F32)
+            launch_pdl(causal_conv_step_kernel<float>, grid, dim3(128), 0, st, x, ldx, in_bias, taps, out_bias, conv_state, (float*)y, ldy, seq_slots, seq_start, channels,
+                       num_taps, act, add_input);
+        else if (out_dtype == B200_BF16)
+            launch_pdl(causal_conv_step_kernel<__nv_bfloat16>, grid, dim3(128), 0, st, x, ldx, in_bias, taps, out_bias, conv_state, (__nv_bfloat16*)y, ldy, seq_slots,
+                       seq_start, channels, num_taps, act, add_input);
+        else { set_error(kErrUnsupported, "causal_conv_ex: out dtype %d (f32 / bf16)", out_dtype); return; }
+        count_launch();
+        check_launch("causal_conv_ex");
+        return;
+    }
     if (out_dtype == B200_F32)
         launch_pdl(causal_conv_ex_kernel<float>, grid, dim3(128), 0, st, x, ldx, in_bias, taps, out_bias, (const float*)conv_state, (float*)y, ldy, token_seq,
                    cu_seqlens, seq_slots, seq_start, channels, num_taps, act, add_input);
@@ -567,9 +727,10 @@ void gated_linear_scan(const float* u, int64_t ldu, float* gates, int64_t ld_gat
 
 void linear_attention(const float* proj, int64_t ld, int32_t off_q, int32_t off_k, int32_t off_v, int32_t off_i, int32_t off_f, const float* decay,
                       const float* i_bias, const float* f_bias, float gate_cap, float q_scale, int32_t act, int32_t gating, float* state, float* normaliser,
-                      float* maximum, float* out, const int32_t* cu_seqlens, const int32_t* seq_slots, const int32_t* seq_start, int32_t num_seqs,
-                      int32_t num_heads, int32_t dk, int32_t dv, int64_t stream) {
+                      float* maximum, float* out, const int32_t* cu_seqlens, const int32_t* seq_slots, const int32_t* seq_start, int32_t num_tokens,
+                      int32_t num_seqs, int32_t single_rows, int32_t num_heads, int32_t dk, int32_t dv, int64_t stream) {
     if (num_seqs == 0) return;
+    B200_REQUIRE(!single_rows || num_tokens == num_seqs, kErrBadArg, "linear_attention: the single-row kernel takes one row per entry");
     B200_REQUIRE(proj && state && out && cu_seqlens && seq_slots && seq_start && num_heads > 0 && num_heads <= 65535 && num_seqs <= 65535 && dk > 0 && dv > 0 &&
                  (act == 0 || act == 1) && (gating == 0 || gating == 1), kErrBadArg, "linear_attention: bad arguments");
     B200_REQUIRE(gating == 0 ? decay != nullptr : (normaliser && maximum && gate_cap > 0.f), kErrBadArg,
@@ -578,8 +739,8 @@ void linear_attention(const float* proj, int64_t ld, int32_t off_q, int32_t off_
     LinAttnArgs A{proj, ld, off_q, off_k, off_v, off_i, off_f, decay, i_bias, f_bias, gate_cap, q_scale, act, state, normaliser, maximum, out,
                   cu_seqlens, seq_slots, seq_start, num_heads, dk, dv};
     cudaStream_t st = as_stream(stream);
-    if (gating == 0) dispatch_linear_attention<false>(A, num_seqs, st);
-    else dispatch_linear_attention<true>(A, num_seqs, st);
+    if (gating == 0) dispatch_linear_attention<false>(A, num_seqs, single_rows != 0, st);
+    else dispatch_linear_attention<true>(A, num_seqs, single_rows != 0, st);
     count_launch();
     check_launch("linear_attention");
 }

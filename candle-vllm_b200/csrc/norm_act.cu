@@ -14,6 +14,7 @@
 //   layer_norm_ex    out[r] = (x[src(r)] - mean) / sqrt(var + eps) * w + b with the biased variance, in up to two copies: one of the
 //                    compute dtype for the next product, one f32 for whatever else reads the normed row;
 //   gated_residual_add  x <- x + sigmoid(z + bias) * y, the gate's pre-activation z being a product of its own (z null: x <- x + y);
+//   gated_add_layer_norm  both of the above in one pass over the row: the closing sum of a sublayer, then the next sublayer's norm of the new x;
 //   glu_packed       out = act(gate) * up from a packed [rows, 2 ff] product, act one of silu, tanh GELU, or the clamped form
 //                    g' = min(g, limit), u' = clamp(u, +-limit), g' sigmoid(1.702 g') (u' + 1); a per-row factor may multiply gate and
 //                    up first (an expert that sees its token times the router's score);
@@ -279,6 +280,36 @@ __global__ void head_gate_kernel(const TS* __restrict__ src, const float* __rest
     out[i] = from_f32<TOut>(to_f32<TS>(src[i]) / (1.0f + expf(-gate[r * ldg + h])));
 }
 
+
+// the closing sum of one sublayer and the opening norm of the next in one pass over the row: x <- x + sigmoid(z + zb) * y, then the layer norm of the new x
+template <typename TOut>
+__global__ void __launch_bounds__(256)
+gated_add_layer_norm_kernel(float* __restrict__ x, const float* __restrict__ y, int64_t ldy, const float* __restrict__ z, int64_t ldz, const float* __restrict__ zb,
+                            const float* __restrict__ w, const float* __restrict__ b, TOut* out, float* out32, int n, float eps) {
+    pdl_wait();
+    pdl_trigger();
+    __shared__ float red[8];
+    const int64_t row = blockIdx.x;
+    float* xr = x + row * n;
+    float s = 0.f;
+    for (int i = threadIdx.x; i < n; i += 256) {
+        float v = y[row * ldy + i];
+        if (z) v *= 1.0f / (1.0f + expf(-(z[row * ldz + i] + (zb ? zb[i] : 0.f))));
+        v += xr[i];
+        xr[i] = v;                                 // read again below by the thread that wrote it
+        s += v;
+    }
+    const float mean = block_sum_256(s, red) / (float)n;
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < n; i += 256) { const float d = xr[i] - mean; ss = fmaf(d, d, ss); }
+    const float sc = 1.0f / sqrtf(block_sum_256(ss, red) / (float)n + eps);
+    for (int i = threadIdx.x; i < n; i += 256) {
+        const float v = fmaf((xr[i] - mean) * sc, w[i], b ? b[i] : 0.f);
+        if (out) out[row * n + i] = from_f32<TOut>(v);
+        if (out32) out32[row * n + i] = v;
+    }
+}
+
 }  // namespace
 }  // namespace b200
 
@@ -456,6 +487,21 @@ void head_gate(const void* src, int32_t src_dtype, const float* gate, int64_t ld
 #undef HG
     count_launch();
     check_launch("head_gate");
+}
+
+void gated_add_layer_norm(float* x, const float* y, int64_t ldy, const float* gate_logits, int64_t ld_gate, const float* gate_bias, const float* weight, const float* bias,
+                          void* out, float* out32, int32_t rows, int32_t n, float eps, int32_t out_dtype, int64_t stream) {
+    if (rows == 0) return;
+    B200_REQUIRE(x && y && weight && (out || out32) && rows > 0 && n > 0 && ldy >= n && (!gate_logits || ld_gate >= n), kErrBadArg, "gated_add_layer_norm: bad arguments");
+    cudaStream_t st = as_stream(stream);
+    if (out_dtype == B200_F32)
+        launch_pdl(gated_add_layer_norm_kernel<float>, dim3(rows), dim3(256), 0, st, x, y, ldy, gate_logits, ld_gate, gate_bias, weight, bias, (float*)out, out32, n, eps);
+    else if (out_dtype == B200_BF16)
+        launch_pdl(gated_add_layer_norm_kernel<__nv_bfloat16>, dim3(rows), dim3(256), 0, st, x, y, ldy, gate_logits, ld_gate, gate_bias, weight, bias, (__nv_bfloat16*)out,
+                   out32, n, eps);
+    else { set_error(kErrUnsupported, "gated_add_layer_norm: out dtype %d (f32 / bf16)", out_dtype); return; }
+    count_launch();
+    check_launch("gated_add_layer_norm");
 }
 
 }  // extern "C"

@@ -182,9 +182,10 @@ class PanaraxModel:
         nothing is wanted)."""
         cfg, dt, D = self.cfg, self.dtype, self.cfg.width
         x = ops.embedding_positional(self.embed, self.pos, batch)
+        pending = None                    # a sublayer's gated output that has not joined the stream yet: the next norm's kernel adds it first
         for li, L in enumerate(self.layers):
             st = state_cache[li]
-            h, h32 = ops.layer_norm(x, L.norm1, L.norm1_b, cfg.eps, dt, also_f32=L.canon is not None)
+            h, h32 = ops.layer_norm(x, L.norm1, L.norm1_b, cfg.eps, dt, also_f32=L.canon is not None, pending=pending)
             z = ops.linear(h, L.rg1) if L.rg1 is not None else None
             if L.canon is not None:
                 hc = ops.causal_conv(h32, L.canon, st[0], batch, out_dtype=dt, add_input=True)
@@ -195,18 +196,22 @@ class PanaraxModel:
                 y = L.mixer.forward(hc, batch, kv_cache[self.kv_index[li]], st)
             else:
                 y = L.mixer.forward(hc, batch, st)
-            ops.gated_residual_add(x, y, z, L.rg1_b)
+            pending = (y, z, L.rg1_b)
             if L.mlp is not None:
-                h = ops.layer_norm(x, L.norm2, L.norm2_b, cfg.eps, dt)
+                h = ops.layer_norm(x, L.norm2, L.norm2_b, cfg.eps, dt, pending=pending)
                 proj = ops.linear(h, L.mlp_in)
                 z = proj[:, :D] if L.has_rg2 else None
                 if isinstance(L.mlp, GatedMlp):
                     y = L.mlp.forward(h, proj=proj[:, L.off_mlp:])
                 else:
                     y = L.mlp.forward(h, x, logits=proj[:, L.off_mlp:])
-                ops.gated_residual_add(x, y, z, L.rg2_b)
+                pending = (y, z, L.rg2_b)
             if hidden_trace is not None:
+                ops.gated_residual_add(x, *pending)
+                pending = None
                 hidden_trace.append(x.clone())
+        if pending is not None:
+            ops.gated_residual_add(x, *pending)
         if batch.num_want == 0:
             return None
         hn = ops.layer_norm(x, self.final_norm, self.final_norm_b, cfg.eps, dt, row_index=batch.want_rows)

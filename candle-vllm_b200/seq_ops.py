@@ -510,15 +510,26 @@ def embedding_positional(table: torch.Tensor, pos_table: torch.Tensor, batch: St
 
 
 def layer_norm(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor], eps: float, out_dtype: torch.dtype, row_index: Optional[torch.Tensor] = None,
-               also_f32: bool = False):
+               also_f32: bool = False, pending: Optional[tuple] = None):
     """Layer norm of f32 rows with weight and bias -> rows of ``out_dtype``; ``also_f32`` returns (out, f32 copy) -- the same tensor twice when
-    out_dtype is f32.  ``row_index`` (i32) selects the rows."""
+    out_dtype is f32.  ``row_index`` (i32) selects the rows.  ``pending`` = (y, gate_logits, gate_bias): the sum x += sigmoid(gate_logits + gate_bias) * y
+    (see ``gated_residual_add``) is done first, in the same kernel, and x (contiguous) is updated in place."""
     n = x.shape[-1]
     rows = x.shape[0] if row_index is None else row_index.shape[0]
     if x.dtype != torch.float32 or weight.dtype != torch.float32 or x.stride(-1) != 1:
         raise BackendError("layer_norm: x and weight are f32")
     out = torch.empty((rows, n), dtype=out_dtype, device=x.device)
     out32 = torch.empty((rows, n), dtype=torch.float32, device=x.device) if also_f32 and out_dtype != torch.float32 else None
+    if pending is not None:
+        y, z, zb = pending
+        T = x.shape[0]
+        if row_index is not None or not x.is_contiguous() or y.dtype != torch.float32 or y.stride(1) != 1 or (z is not None and z.stride(1) != 1):
+            raise BackendError("layer_norm: a pending sum needs the whole contiguous stream and f32 operands")
+        pitch = lambda t: t.stride(0) if T > 1 else max(n, t.stride(0))
+        lib().gated_add_layer_norm(_ptr(x), _ptr(y), C.c_int64(pitch(y)), _ptr(z), C.c_int64(0 if z is None else pitch(z)), _ptr(zb), _ptr(weight), _ptr(bias), _ptr(out),
+                                   _ptr(out32), C.c_int32(T), C.c_int32(n), C.c_float(eps), C.c_int32(_tag(out_dtype)), _stream(x.device))
+        check("gated_add_layer_norm")
+        return (out, (out if out32 is None else out32)) if also_f32 else out
     lib().layer_norm_ex(_ptr(x), _ptr(weight), _ptr(bias), _ptr(out), _ptr(out32), _ptr(row_index), C.c_int32(rows), C.c_int32(n),
                         C.c_int64(x.stride(0) if x.shape[0] > 1 else n), C.c_float(eps), C.c_int32(_tag(out_dtype)), _stream(x.device))
     check("layer_norm_ex")
@@ -590,7 +601,7 @@ def causal_conv(x: torch.Tensor, taps: torch.Tensor, conv_state: torch.Tensor, b
     y = torch.empty((T, Cn), dtype=out_dtype, device=x.device)
     lib().causal_conv_ex(_ptr(x), C.c_int64(x.stride(0) if T > 1 else max(Cn, x.stride(0))), _ptr(in_bias), _ptr(taps), _ptr(out_bias), _ptr(conv_state), _ptr(y),
                          C.c_int64(Cn), _ptr(batch.token_seq), _ptr(batch.cu_seqlens), _ptr(batch.seq_slots), _ptr(batch.seq_start), C.c_int32(T),
-                         C.c_int32(batch.num_seqs), C.c_int32(Cn), C.c_int32(K), C.c_int32({"none": 0, "silu": 1}[act]), C.c_int32(1 if add_input else 0),
+                         C.c_int32(batch.num_seqs), C.c_int32(1 if batch.pure_decode else 0), C.c_int32(Cn), C.c_int32(K), C.c_int32({"none": 0, "silu": 1}[act]), C.c_int32(1 if add_input else 0),
                          C.c_int32(_tag(out_dtype)), _stream(x.device))
     check("causal_conv_ex")
     return y
@@ -637,6 +648,7 @@ def linear_attention(proj: torch.Tensor, off_q: int, off_k: int, off_v: int, sta
                            C.c_int32(g.get("off_i", 0)), C.c_int32(g.get("off_f", 0)), _ptr(decay), _ptr(g.get("i_bias")), _ptr(g.get("f_bias")),
                            C.c_float(g.get("cap", 0.0)), C.c_float(q_scale), C.c_int32({"none": 0, "silu": 1}[act]), C.c_int32(0 if gates is None else 1), _ptr(state),
                            _ptr(g.get("normaliser")), _ptr(g.get("maximum")), _ptr(out), _ptr(batch.cu_seqlens), _ptr(batch.seq_slots), _ptr(batch.seq_start),
-                           C.c_int32(batch.num_seqs), C.c_int32(heads), C.c_int32(dk), C.c_int32(dv), _stream(proj.device))
+                           C.c_int32(T), C.c_int32(batch.num_seqs), C.c_int32(1 if batch.pure_decode else 0), C.c_int32(heads), C.c_int32(dk), C.c_int32(dv),
+                           _stream(proj.device))
     check("linear_attention")
     return out

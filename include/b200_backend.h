@@ -568,6 +568,7 @@ void moe_down(const void* act, const void* w_down, const int32_t* ids, const int
  * layer_norm_ex: (x[src] - mean) / sqrt(var + eps) * weight + bias (bias may be null), biased variance, src = row_index ? row_index[r] : r; written
  *   to out (out_dtype F32 / BF16; may be null) and / or out32 (f32; may be null).
  * gated_residual_add: x[r, c] += sigmoid(gate_logits[r, c] + gate_bias[c]) * y[r, c] in place on the f32 stream; gate_logits null: x += y.
+ * gated_add_layer_norm: gated_residual_add on the contiguous f32 stream x [rows, n], then layer_norm_ex of the new rows (no row_index), in one kernel.
  * glu_packed: out[r, :ff] = act(g) * u from f32 gate_up [rows, ff | ff] (row pitch ld); act 0 = SiLU, 1 = tanh GELU, 2 = clamped: g' = min(g, limit),
  *   u' = clamp(u, -limit, limit), out = g' sigmoid(1.702 g') (u' + 1).  row_scale (f32, may be null) multiplies g and u first: row r takes
  *   row_scale[scale_index ? scale_index[r] : r]; a negative index marks a padding row, written as zeros.
@@ -577,7 +578,8 @@ void moe_down(const void* act, const void* w_down, const int32_t* ids, const int
  *   source goes to a BF16 out).
  * causal_conv_ex: y[t, c] = act(sum_j taps[c, j] in[t - K + 1 + j, c] + out_bias[c]) (+ in[t, c] when add_input), in = x + in_bias (zeros before a
  *   sequence's start); conv_state f32 [slots, max(K - 1, 1), channels] holds a sequence's last K - 1 inputs and is rolled forward.  act 0 = none,
- *   1 = SiLU; y of out_dtype F32 / BF16 with row pitch ldy.
+ *   1 = SiLU; y of out_dtype F32 / BF16 with row pitch ldy.  single_rows != 0 (every entry brings exactly one row, row b belongs to entry b): one
+ *   kernel does the convolution and the roll.
  * block_diag_linear: out[t, b M + j] = sum_i weight[b, j, i] x[t, b N + i] + bias[b M + j], M = rows_per_block, N = cols_per_block; all f32, true
  *   32-bit products.
  * gated_linear_scan: per channel c of block c / block_channels: r = sigmoid(gates[t, blk, j]), i = sigmoid(gates[t, blk, n + j]) (gates f32 [T, blocks,
@@ -589,7 +591,7 @@ void moe_down(const void* act, const void* w_down, const int32_t* ids, const int
  *   tanh((proj[off_i + h] + i_bias[h]) / cap), f = logsigmoid(cap tanh((proj[off_f + h] + f_bias[h]) / cap)) and the running maximum m (0 at the
  *   start) m' = max(f + m, i): a = e^(f + m - m'), b = e^(i - m'), normaliser n <- a n + b k, o = S^T q / (max(|n . q|, e^(-m')) + 1e-6);
  *   normaliser f32 [slots, H, ceil(dv / 16), dk] and maximum f32 [slots, H, ceil(dv / 16)] (one copy per block of 16 value columns).  out f32
- *   [T, H dv].  dk <= 256.
+ *   [T, H dv].  dk <= 256.  single_rows != 0 (every entry brings exactly one row): a kernel that stages nothing and takes one pass over the state.
  * qk_norm_rope_cache_ex: qk_norm_rope_cache plus a query temperature (q times 1 + q_temp_coef ln(floor((p + 1) / q_temp_every) + 1); every 0 = off)
  *   and, with v_unit_rms, values divided by their root mean square per head (eps inside the root) before they are cached.
  * moe_route_ex: moe_route with score_fn 0 = softmax, 1 = sigmoid per output, and normalise 0 = the chosen scores times scale as they are.
@@ -601,6 +603,8 @@ void layer_norm_ex(const float* x, const float* weight, const float* bias, void*
                    float eps, int32_t out_dtype, int64_t stream);
 void gated_residual_add(float* x, const float* y, int64_t ldy, const float* gate_logits, int64_t ld_gate, const float* gate_bias, int32_t rows, int32_t n,
                         int64_t stream);
+void gated_add_layer_norm(float* x, const float* y, int64_t ldy, const float* gate_logits, int64_t ld_gate, const float* gate_bias, const float* weight, const float* bias,
+                          void* out, float* out32, int32_t rows, int32_t n, float eps, int32_t out_dtype, int64_t stream);
 void glu_packed(const float* gate_up, void* out, int64_t rows, int32_t ff, int64_t ld, int32_t act, float limit, const float* row_scale, const int32_t* scale_index,
                 int32_t out_dtype, int64_t stream);
 void group_rms_norm_gate(const float* o, int64_t ldo, const float* weight, const float* gate, int64_t ld_gate, void* out, int32_t num_tokens, int32_t n,
@@ -609,7 +613,7 @@ void head_gate(const void* src, int32_t src_dtype, const float* gate, int64_t ld
                int64_t stream);
 void causal_conv_ex(const float* x, int64_t ldx, const float* in_bias, const float* taps, const float* out_bias, float* conv_state, void* y, int64_t ldy,
                     const int32_t* token_seq, const int32_t* cu_seqlens, const int32_t* seq_slots, const int32_t* seq_start, int32_t num_tokens,
-                    int32_t num_seqs, int32_t channels, int32_t num_taps, int32_t act, int32_t add_input, int32_t out_dtype, int64_t stream);
+                    int32_t num_seqs, int32_t single_rows, int32_t channels, int32_t num_taps, int32_t act, int32_t add_input, int32_t out_dtype, int64_t stream);
 void block_diag_linear(const float* x, int64_t ldx, const float* weight, const float* bias, float* out, int64_t ldy, int32_t num_tokens, int32_t blocks,
                        int32_t rows_per_block, int32_t cols_per_block, int64_t stream);
 void gated_linear_scan(const float* u, int64_t ldu, float* gates, int64_t ld_gates, const float* lam, float* y_pre, int64_t ldy, const float* y_bias,
@@ -617,8 +621,8 @@ void gated_linear_scan(const float* u, int64_t ldu, float* gates, int64_t ld_gat
                        int32_t max_rows, int32_t channels, int32_t block_channels, float decay_scale, int32_t out_dtype, int64_t stream);
 void linear_attention(const float* proj, int64_t ld, int32_t off_q, int32_t off_k, int32_t off_v, int32_t off_i, int32_t off_f, const float* decay,
                       const float* i_bias, const float* f_bias, float gate_cap, float q_scale, int32_t act, int32_t gating, float* state, float* normaliser,
-                      float* maximum, float* out, const int32_t* cu_seqlens, const int32_t* seq_slots, const int32_t* seq_start, int32_t num_seqs,
-                      int32_t num_heads, int32_t dk, int32_t dv, int64_t stream);
+                      float* maximum, float* out, const int32_t* cu_seqlens, const int32_t* seq_slots, const int32_t* seq_start, int32_t num_tokens,
+                      int32_t num_seqs, int32_t single_rows, int32_t num_heads, int32_t dk, int32_t dv, int64_t stream);
 void qk_norm_rope_cache_ex(const float* qkv, int64_t ld, const float* q_norm_w, const float* k_norm_w, const float* cos_t, const float* sin_t,
                            int32_t max_pos, const int32_t* positions, const int64_t* slot_mapping, void* q_out, void* key_cache, void* value_cache,
                            int32_t num_tokens, int32_t num_heads, int32_t num_kv_heads, int32_t dk, int32_t dv, int32_t rot_dims, float eps,

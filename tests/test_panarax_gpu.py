@@ -95,6 +95,16 @@ def test_layer_norm(n):
     close(o16, want, 6e-3, "bf16 copy"); close(o32, want, 2e-6, "f32 copy")
     idx = torch.tensor([6, 0, 3], dtype=torch.int32)
     close(ops.layer_norm(dev(x), dev(w), dev(b), 1e-5, torch.float32, row_index=idx.to(DEV)), want[idx.long()], 2e-6, "gathered rows")
+    # the closing sum of the sublayer before, done by the norm's own kernel: x is updated in place
+    y, z, zb = torch.randn(7, n + 5, generator=g), torch.randn(7, n, generator=g), torch.randn(n, generator=g)
+    x_new = x.to(F64) + torch.sigmoid(z.to(F64) + zb.to(F64)) * y[:, 5:].to(F64)
+    xd = dev(x)
+    o16, o32 = ops.layer_norm(xd, dev(w), dev(b), 1e-5, BF, also_f32=True, pending=(dev(y)[:, 5:], dev(z), dev(zb)))
+    close(xd, x_new, 2e-6, "stream after the pending sum")
+    close(o32, P.layer_norm(x_new, w.to(F64), b.to(F64), 1e-5), 3e-6, "norm of the new stream"); close(o16, o32, 6e-3, "its bf16 copy")
+    xd = dev(x)
+    close(ops.layer_norm(xd, dev(w), dev(b), 1e-5, torch.float32, pending=(dev(y)[:, 5:], None, None)), P.layer_norm(x.to(F64) + y[:, 5:].to(F64), w.to(F64), b.to(F64), 1e-5),
+          3e-6, "ungated pending sum")
     # a large common offset must not leak into the variance
     close(ops.layer_norm(dev(x + 300.0), dev(w), dev(b), 1e-5, torch.float32), P.layer_norm((x + 300.0).to(F64), w.to(F64), b.to(F64), 1e-5), 2e-4, "offset rows")
 
