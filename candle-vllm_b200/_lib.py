@@ -38,7 +38,7 @@ SYMBOLS = [
     "qk_norm_rope_cache", "paged_attention_varlen", "chunk_decode_view",
     "embedding_bigram", "residual_rms_norm", "gelu_tanh_gather_mul", "latent_kv_rope_cache", "latent_q_absorb", "latent_attention_varlen", "latent_out_gate", "moe_route", "moe_gate_up", "moe_down", "mla_decode_kernel_supported", "mla_paged_attention_sink", "repack_heads", "token_tables", "linear_grouped", "moe_align_rows", "moe_align", "moe_gather_rows", "silu_mul_packed", "moe_combine_rows",
     "embedding_positional", "layer_norm_ex", "gated_residual_add", "gated_add_layer_norm", "glu_packed", "group_rms_norm_gate", "head_gate", "causal_conv_ex", "block_diag_linear", "gated_linear_scan",
-    "linear_attention", "qk_norm_rope_cache_ex", "moe_route_ex", "moe_gate_up_ex",
+    "linear_attention", "linear_attention_chunked", "linear_attention_chunked_scratch", "qk_norm_rope_cache_ex", "moe_route_ex", "moe_gate_up_ex",
 ]
 
 
@@ -53,7 +53,7 @@ GROUP_SYMBOLS = {
                          "latent_out_gate", "moe_route", "moe_gate_up", "moe_down", "mla_decode_kernel_supported", "mla_paged_attention_sink",
                          "mla_paged_decode_workspace_bytes", "repack_heads", "token_tables", "linear_grouped", "moe_align_rows", "moe_align", "moe_gather_rows", "silu_mul_packed",
                          "moe_combine_rows"],
-    "hybrid": _COMMON + ["causal_conv_ex", "block_diag_linear", "gated_linear_scan", "linear_attention", "qk_norm_rope_cache", "qk_norm_rope_cache_ex",
+    "hybrid": _COMMON + ["causal_conv_ex", "block_diag_linear", "gated_linear_scan", "linear_attention", "linear_attention_chunked", "linear_attention_chunked_scratch", "qk_norm_rope_cache", "qk_norm_rope_cache_ex",
                          "paged_attention_varlen", "chunk_decode_view", "paged_attention_decode", "paged_attention_decode_workspace_bytes", "moe_route", "moe_route_ex", "moe_gate_up", "moe_gate_up_ex", "moe_down", "linear_grouped",
                          "moe_align_rows", "moe_align", "moe_gather_rows", "silu_mul_packed", "moe_combine_rows"],
 }
@@ -61,7 +61,7 @@ _RESTYPES = {"b200_last_error_message": C.c_char_p, "paged_attention_decode_work
              "moe_gemm_workspace_bytes": C.c_size_t, "moe_gemm_fp8_workspace_bytes": C.c_size_t, "mla_paged_decode_workspace_bytes": C.c_size_t,
              "b200_llama_create": C.c_void_p, "b200_llama_peer_inbox_bytes": C.c_size_t, "b200_ipc_alloc": C.c_void_p, "b200_ipc_open": C.c_void_p,
              "b200_llama_logits": C.c_void_p, "b200_llama_next_tokens": C.c_void_p, "b200_llama_kernel_launches": C.c_int64,
-             "b200_total_kernel_launches": C.c_longlong, "moe_align_rows": C.c_int64}
+             "b200_total_kernel_launches": C.c_longlong, "moe_align_rows": C.c_int64, "linear_attention_chunked_scratch": C.c_int64}
 
 
 def _open(path: str, symbols) -> C.CDLL:

@@ -608,6 +608,370 @@ linear_attention_step_kernel(const LinAttnArgs A) {
     if (kExp && threadIdx.x == 0) A.mx[own] = m_new;
 }
 
+// ---- portions of prompts: the same recurrence over chunks of 64 tokens, all chunks at once -----------------------------------------------------
+// With F_t the sum of the log decays from the chunk's first token to t, li_t the log input weight and m_t the running maximum (F_t = (t + 1) ln decay,
+// li = 0, m = 0 for a fixed decay), token t of a chunk that is entered with the (stabilised) state S_in and maximum m_in returns
+//     o_t = e^(F_t + m_in - m_t) S_in^T q_t + sum_{j <= t} e^(F_t - F_j + li_j - m_t) (q_t . k_j) v_j
+// and the chunk leaves  S_out = e^(F_L + m_in - m_L) S_in + sum_j e^(F_L - F_j + li_j - m_L) k_j v_j^T  (the normaliser alike, with k_j alone).  So:
+//   la_gate_values   (exponential gating) log gates of every token, all rows at once;
+//   la_gate_chain    per (entry, head) the chain of maxima m_t, exactly as the token-by-token kernel takes it, and F_t;
+//   la_chunk_state   per chunk the second term of S_out, a [dv, dk] product over the chunk's tokens, all chunks at once;
+//   la_chunk_scan    per state element the walk over an entry's chunks that turns those terms into the state entering every chunk (in place);
+//   la_chunk_output  per chunk the two terms of o_t: scores against the chunk's own keys, then values and entering state in one accumulation.
+// All arithmetic is f32 on the FMA pipe; the results differ from the token-by-token kernel by rounding only.
+constexpr int kChunk = 64;
+
+struct ChunkArgs {
+    LinAttnArgs A;
+    float* gc;            // [T, H, 3]: F_t, li_t, m_t (exponential gating)
+    float* U;             // [chunk slots, H, dv, dk]
+    float* un;            // [chunk slots, H, dk] a chunk's own term of the normaliser
+    float* un_in;         // [chunk slots, H, dk] the normaliser that enters the chunk
+    float* m0;            // [entries, H] the maximum every entry starts this step with (the slot's copy changes while the kernels run)
+    int max_chunks;       // the most chunks any entry has
+    int gating;
+};
+
+__device__ __forceinline__ int chunk_base(const int32_t* cu, int b) {      // chunk slots of the entries before b
+    int s = 0;
+    for (int i = 0; i < b; ++i) s += (cu[i + 1] - cu[i] + kChunk - 1) / kChunk;
+    return s;
+}
+__device__ __forceinline__ float log_decay(float d) { return fmaxf(logf(d), -80.f); }
+
+__global__ void la_gate_values_kernel(const ChunkArgs C, int T) {
+    pdl_wait();
+    pdl_trigger();
+    const LinAttnArgs& A = C.A;
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= T * A.H) return;
+    const int t = i / A.H, h = i - t * A.H;
+    const float* row = A.proj + (int64_t)t * A.ld;
+    const float zi = row[A.off_i + h] + (A.i_bias ? A.i_bias[h] : 0.f), zf = row[A.off_f + h] + (A.f_bias ? A.f_bias[h] : 0.f);
+    C.gc[(int64_t)i * 3 + 1] = A.cap * tanhf(zi / A.cap);
+    C.gc[(int64_t)i * 3 + 0] = log_sigmoid_f(A.cap * tanhf(zf / A.cap));
+}
+
+__global__ void la_gate_chain_kernel(const ChunkArgs C) {
+    pdl_wait();
+    pdl_trigger();
+    const LinAttnArgs& A = C.A;
+    const int h = blockIdx.x * blockDim.x + threadIdx.x, b = blockIdx.y;
+    if (h >= A.H) return;
+    const int t0 = A.cu_seqlens[b], t1 = A.cu_seqlens[b + 1];
+    if (t1 <= t0) return;
+    const int nvb = (A.dv + 15) / 16;
+    float m = A.seq_start[b] == 0 ? 0.f : A.mx[((int64_t)A.seq_slots[b] * A.H + h) * nvb];
+    C.m0[(int64_t)b * A.H + h] = m;
+    float F = 0.f;
+    // the chain itself is an add and a maximum per token; the log gates of the next sixteen tokens are in flight meanwhile
+    constexpr int kAhead = 16;
+    float nf[kAhead], ni[kAhead];
+    float* g0 = C.gc + (int64_t)h * 3;
+    const int64_t pitch = (int64_t)A.H * 3;
+#pragma unroll
+    for (int a = 0; a < kAhead; ++a) { const int64_t t = min(t0 + a, t1 - 1); nf[a] = g0[t * pitch]; ni[a] = g0[t * pitch + 1]; }
+    for (int tb = t0; tb < t1; tb += kAhead) {
+        float cf[kAhead], ci[kAhead];
+#pragma unroll
+        for (int a = 0; a < kAhead; ++a) { cf[a] = nf[a]; ci[a] = ni[a]; }
+#pragma unroll
+        for (int a = 0; a < kAhead; ++a) { const int64_t t = min(tb + kAhead + a, t1 - 1); nf[a] = g0[t * pitch]; ni[a] = g0[t * pitch + 1]; }
+#pragma unroll
+        for (int a = 0; a < kAhead; ++a) {
+            const int t = tb + a;
+            if (t >= t1) break;
+            if ((t - t0) % kChunk == 0) F = 0.f;
+            F += cf[a];
+            m = fmaxf(cf[a] + m, ci[a]);
+            g0[(int64_t)t * pitch] = F; g0[(int64_t)t * pitch + 2] = m;
+        }
+    }
+}
+
+// F, li, m of row t (tt = its index inside the chunk)
+__device__ __forceinline__ void token_gate(const ChunkArgs& C, int h, int t, int tt, float lnd, float& F, float& li, float& m) {
+    if (C.gating == 0) { F = (float)(tt + 1) * lnd; li = 0.f; m = 0.f; return; }
+    const float* g = C.gc + ((int64_t)t * C.A.H + h) * 3;
+    F = g[0]; li = g[1]; m = g[2];
+}
+__device__ __forceinline__ float chunk_m_in(const ChunkArgs& C, int b, int h, int t_first, int c) {
+    if (C.gating == 0) return 0.f;
+    if (c > 0) return C.gc[((int64_t)(t_first - 1) * C.A.H + h) * 3 + 2];
+    return C.m0[(int64_t)b * C.A.H + h];
+}
+
+// U[slot, h, cv, r] = sum_j w_j v_j[cv] k_j[r], w_j = e^(F_L - F_j + li_j - m_L); a block makes a 64 x 64 tile, a thread 4 x 4 of it
+__global__ void __launch_bounds__(256)
+la_chunk_state_kernel(const ChunkArgs C) {
+    pdl_wait();
+    pdl_trigger();
+    const LinAttnArgs& A = C.A;
+    __shared__ __align__(16) float vs[kChunk][64 + 4], ks[kChunk][64 + 4];          // rows of 68 floats: 16-byte reads of four neighbours
+    __shared__ float ws[kChunk];
+    const int h = blockIdx.y, b = blockIdx.z / C.max_chunks, c = blockIdx.z % C.max_chunks;
+    const int t0 = A.cu_seqlens[b], rows = A.cu_seqlens[b + 1] - t0;
+    if (c * kChunk >= rows) return;
+    const int tf = t0 + c * kChunk, nt = min(kChunk, rows - c * kChunk);
+    const int dk = A.dk, dv = A.dv, H = A.H;
+    const int tiles_r = (dk + 63) / 64;
+    const int cv0 = (blockIdx.x / tiles_r) * 64, r0 = (blockIdx.x % tiles_r) * 64;
+    const int slot = chunk_base(A.cu_seqlens, b) + c;
+    const float lnd = C.gating == 0 ? log_decay(A.decay[h]) : 0.f;
+    if (threadIdx.x < kChunk) {
+        float w = 0.f;
+        if ((int)threadIdx.x < nt) {
+            float F, li, m, FL, liL, mL;
+            token_gate(C, h, tf + threadIdx.x, threadIdx.x, lnd, F, li, m);
+            token_gate(C, h, tf + nt - 1, nt - 1, lnd, FL, liL, mL);
+            w = expf(FL - F + li - mL);
+        }
+        ws[threadIdx.x] = w;
+    }
+    __syncthreads();
+    for (int e = threadIdx.x; e < kChunk * 64; e += 256) {
+        const int j = e >> 6, x = e & 63;
+        float v = 0.f, k = 0.f;
+        if (j < nt) {
+            const float* row = A.proj + (int64_t)(tf + j) * A.ld;
+            if (cv0 + x < dv) { v = row[A.off_v + h * dv + cv0 + x]; if (A.act == 1) v = silu_f(v); }
+            if (r0 + x < dk) { k = row[A.off_k + h * dk + r0 + x]; if (A.act == 1) k = silu_f(k); }
+        }
+        vs[j][x] = v * ws[j]; ks[j][x] = k;
+    }
+    __syncthreads();
+    const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;
+    float acc[4][4] = {};
+    for (int j = 0; j < nt; ++j) {
+        const float4 a4 = *reinterpret_cast<const float4*>(&vs[j][ty * 4]), k4 = *reinterpret_cast<const float4*>(&ks[j][tx * 4]);
+        const float a[4] = {a4.x, a4.y, a4.z, a4.w}, k[4] = {k4.x, k4.y, k4.z, k4.w};
+#pragma unroll
+        for (int i = 0; i < 4; ++i)
+#pragma unroll
+            for (int l = 0; l < 4; ++l) acc[i][l] = fmaf(a[i], k[l], acc[i][l]);
+    }
+    float* U = C.U + ((int64_t)slot * H + h) * dv * dk;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const int cv = cv0 + ty * 4 + i;
+        if (cv >= dv) continue;
+#pragma unroll
+        for (int l = 0; l < 4; ++l) {
+            const int r = r0 + tx * 4 + l;
+            if (r < dk) U[(int64_t)cv * dk + r] = acc[i][l];
+        }
+    }
+    if (C.gating == 1 && cv0 == 0 && threadIdx.x < 64 && r0 + (int)threadIdx.x < dk) {
+        float s = 0.f;
+        for (int j = 0; j < nt; ++j) s = fmaf(ws[j], ks[j][threadIdx.x], s);
+        C.un[((int64_t)slot * H + h) * dk + r0 + threadIdx.x] = s;
+    }
+}
+
+// a thread owns one state element (h, cv, r): U[c] <- the state that enters chunk c, the state slot <- the state after the last chunk
+__global__ void __launch_bounds__(256)
+la_chunk_scan_kernel(const ChunkArgs C) {
+    pdl_wait();
+    pdl_trigger();
+    const LinAttnArgs& A = C.A;
+    const int b = blockIdx.y;
+    const int dk = A.dk, dv = A.dv, H = A.H;
+    const int64_t e = (int64_t)blockIdx.x * 256 + threadIdx.x;
+    if (e >= (int64_t)H * dv * dk) return;
+    const int h = (int)(e / ((int64_t)dv * dk));
+    const int cv = (int)((e / dk) % dv), r = (int)(e % dk);
+    const int t0 = A.cu_seqlens[b], rows = A.cu_seqlens[b + 1] - t0;
+    if (rows <= 0) return;
+    const int nc = (rows + kChunk - 1) / kChunk;
+    const int base = chunk_base(A.cu_seqlens, b);
+    const bool fresh = A.seq_start[b] == 0;
+    const int64_t slot = A.seq_slots[b];
+    const int nvb = (dv + 15) / 16;
+    float* Sp = A.S + ((slot * H + h) * dv + cv) * (int64_t)dk + r;
+    const bool carries_n = C.gating == 1 && (cv & 15) == 0;            // one copy of the normaliser and of the maximum per 16 value columns
+    float* np = carries_n ? A.nrm + ((slot * H + h) * nvb + (cv >> 4)) * (int64_t)dk + r : nullptr;
+    float S = fresh ? 0.f : *Sp;
+    float n = (carries_n && !fresh) ? *np : 0.f;
+    const float lnd = C.gating == 0 ? log_decay(A.decay[h]) : 0.f;
+    float m_in = chunk_m_in(C, b, h, t0, 0);
+    // a chunk's term does not depend on the walk: the terms of the next eight chunks are in flight while the current one is applied
+    constexpr int kAhead = 8;
+    const int64_t ustride = (int64_t)H * dv * dk, nstride = (int64_t)H * dk;
+    float* u0 = C.U + (((int64_t)base * H + h) * dv + cv) * dk + r;
+    const int64_t n0 = ((int64_t)base * H + h) * dk + r;
+    float nu[kAhead], nn[kAhead];
+#pragma unroll
+    for (int a = 0; a < kAhead; ++a) {
+        const int c = min(a, nc - 1);
+        nu[a] = u0[c * ustride];
+        nn[a] = carries_n ? C.un[n0 + c * nstride] : 0.f;
+    }
+    for (int cb = 0; cb < nc; cb += kAhead) {
+        float cu[kAhead], cn[kAhead];
+#pragma unroll
+        for (int a = 0; a < kAhead; ++a) { cu[a] = nu[a]; cn[a] = nn[a]; }
+#pragma unroll
+        for (int a = 0; a < kAhead; ++a) {
+            const int c = min(cb + kAhead + a, nc - 1);
+            nu[a] = u0[c * ustride];
+            nn[a] = carries_n ? C.un[n0 + c * nstride] : 0.f;
+        }
+#pragma unroll
+        for (int a = 0; a < kAhead; ++a) {
+            const int c = cb + a;
+            if (c >= nc) break;
+            const int nt = min(kChunk, rows - c * kChunk);
+            float FL, liL, mL;
+            token_gate(C, h, t0 + c * kChunk + nt - 1, nt - 1, lnd, FL, liL, mL);
+            const float g = expf(FL + m_in - mL);
+            u0[c * ustride] = S;
+            S = fmaf(g, S, cu[a]);
+            if (carries_n) {
+                if (cv == 0) C.un_in[n0 + c * nstride] = n;               // the output kernel reads the entering normaliser from here
+                n = fmaf(g, n, cn[a]);
+            }
+            m_in = mL;
+        }
+    }
+    *Sp = S;
+    if (carries_n) {
+        *np = n;
+        if (r == 0) A.mx[(slot * H + h) * nvb + (cv >> 4)] = m_in;
+    }
+}
+
+// o for the 64 tokens of a chunk and 64 value columns: scores against the chunk's own keys, weights, then values and entering state
+__global__ void __launch_bounds__(256)
+la_chunk_output_kernel(const ChunkArgs C) {
+    pdl_wait();
+    pdl_trigger();
+    const LinAttnArgs& A = C.A;
+    extern __shared__ __align__(16) float sm[];
+    // every tile is stored so that the four neighbours a thread multiplies together are one 16-byte read (rows of 68 floats)
+    float (*qs)[68] = reinterpret_cast<float (*)[68]>(sm);                          // [32][68] a slab of 32 key rows of q: [key row][token]
+    float (*ks)[68] = reinterpret_cast<float (*)[68]>(sm + 32 * 68);                // [32][68] the same slab of k: [key row][token]; later of the entering state
+    float (*pw)[68] = reinterpret_cast<float (*)[68]>(sm + 2 * 32 * 68);            // [64][68] weighted scores: [key token j][query token t]
+    float (*vs)[68] = reinterpret_cast<float (*)[68]>(sm + 2 * 32 * 68 + 64 * 68);  // [64][68] values: [token][column]
+    float* sF = sm + 2 * 32 * 68 + 2 * 64 * 68;                                     // [64] F_t, li_t, m_t, c_t, n_in . q_t
+    float* sL = sF + 64; float* sM = sL + 64; float* sC = sM + 64; float* sN = sC + 64;
+    const int h = blockIdx.y, b = blockIdx.z / C.max_chunks, c = blockIdx.z % C.max_chunks;
+    const int t0 = A.cu_seqlens[b], rows = A.cu_seqlens[b + 1] - t0;
+    if (c * kChunk >= rows) return;
+    const int tf = t0 + c * kChunk, nt = min(kChunk, rows - c * kChunk);
+    const int dk = A.dk, dv = A.dv, H = A.H;
+    const int cv0 = blockIdx.x * 64;
+    const int slot = chunk_base(A.cu_seqlens, b) + c;
+    const float lnd = C.gating == 0 ? log_decay(A.decay[h]) : 0.f;
+    const float m_in = chunk_m_in(C, b, h, tf, c);
+    const float* Uin = C.U + ((int64_t)slot * H + h) * dv * dk;
+    const float* nin = C.un_in + ((int64_t)slot * H + h) * dk;
+    if (threadIdx.x < 64) {
+        float F = 0.f, li = 0.f, m = 0.f, nq = 0.f;
+        if ((int)threadIdx.x < nt) {
+            token_gate(C, h, tf + threadIdx.x, threadIdx.x, lnd, F, li, m);
+            if (C.gating == 1) {
+                const float* row = A.proj + (int64_t)(tf + threadIdx.x) * A.ld + A.off_q + h * dk;
+                for (int r = 0; r < dk; ++r) nq = fmaf(nin[r], (A.act == 1 ? silu_f(row[r]) : row[r]) * A.q_scale, nq);
+            }
+        }
+        sF[threadIdx.x] = F; sL[threadIdx.x] = li; sM[threadIdx.x] = m; sC[threadIdx.x] = expf(F + m_in - m); sN[threadIdx.x] = nq;
+    }
+    const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;
+    float acc[4][4] = {};
+    // scores: rows ty * 4 .., keys tx * 4 ..
+    for (int r0 = 0; r0 < dk; r0 += 32) {
+        __syncthreads();
+        for (int e = threadIdx.x; e < 64 * 32; e += 256) {
+            const int j = e >> 5, x = e & 31;
+            float q = 0.f, k = 0.f;
+            if (j < nt && r0 + x < dk) {
+                const float* row = A.proj + (int64_t)(tf + j) * A.ld;
+                q = row[A.off_q + h * dk + r0 + x]; k = row[A.off_k + h * dk + r0 + x];
+                if (A.act == 1) { q = silu_f(q); k = silu_f(k); }
+                q *= A.q_scale;
+            }
+            qs[x][j] = q; ks[x][j] = k;
+        }
+        __syncthreads();
+#pragma unroll 8
+        for (int x = 0; x < 32; ++x) {
+            const float4 a4 = *reinterpret_cast<const float4*>(&qs[x][ty * 4]), k4 = *reinterpret_cast<const float4*>(&ks[x][tx * 4]);
+            const float a[4] = {a4.x, a4.y, a4.z, a4.w}, k[4] = {k4.x, k4.y, k4.z, k4.w};
+#pragma unroll
+            for (int i = 0; i < 4; ++i)
+#pragma unroll
+                for (int l = 0; l < 4; ++l) acc[i][l] = fmaf(a[i], k[l], acc[i][l]);
+        }
+    }
+#pragma unroll
+    for (int l = 0; l < 4; ++l) {
+        const int j = tx * 4 + l;
+        float w[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const int t = ty * 4 + i;
+            w[i] = (j <= t && t < nt) ? acc[i][l] * expf(sF[t] - sF[j] + sL[j] - sM[t]) : 0.f;
+        }
+        *reinterpret_cast<float4*>(&pw[j][ty * 4]) = make_float4(w[0], w[1], w[2], w[3]);
+    }
+    for (int e = threadIdx.x; e < 64 * 64; e += 256) {
+        const int j = e >> 6, x = e & 63;
+        float v = 0.f;
+        if (j < nt && cv0 + x < dv) { v = A.proj[(int64_t)(tf + j) * A.ld + A.off_v + h * dv + cv0 + x]; if (A.act == 1) v = silu_f(v); }
+        vs[j][x] = v;
+    }
+    __syncthreads();
+    // first term of the output: weighted scores times values (rows ty * 4 .., columns tx * 4 ..)
+    float o1[4][4] = {}, o2[4][4] = {};
+    for (int j = 0; j < nt; ++j) {
+        const float4 p4 = *reinterpret_cast<const float4*>(&pw[j][ty * 4]), v4 = *reinterpret_cast<const float4*>(&vs[j][tx * 4]);
+        const float p[4] = {p4.x, p4.y, p4.z, p4.w}, v[4] = {v4.x, v4.y, v4.z, v4.w};
+#pragma unroll
+        for (int i = 0; i < 4; ++i)
+#pragma unroll
+            for (int l = 0; l < 4; ++l) o1[i][l] = fmaf(p[i], v[l], o1[i][l]);
+    }
+    // second term: q against the state that entered the chunk, a slab of 32 key rows at a time
+    float (*ss)[68] = ks;                                                           // [32][68] the entering state: [key row][column], over the k slab
+    for (int r0 = 0; r0 < dk; r0 += 32) {
+        __syncthreads();
+        for (int e = threadIdx.x; e < 64 * 32; e += 256) {
+            const int j = e >> 5, x = e & 31;
+            float q = 0.f;
+            if (j < nt && r0 + x < dk) { q = A.proj[(int64_t)(tf + j) * A.ld + A.off_q + h * dk + r0 + x]; if (A.act == 1) q = silu_f(q); q *= A.q_scale; }
+            qs[x][j] = q;
+            // the same index pair read the other way: column j of the tile, key row x
+            ss[x][j] = (cv0 + j < dv && r0 + x < dk) ? Uin[(int64_t)(cv0 + j) * dk + r0 + x] : 0.f;
+        }
+        __syncthreads();
+#pragma unroll 8
+        for (int x = 0; x < 32; ++x) {
+            const float4 a4 = *reinterpret_cast<const float4*>(&qs[x][ty * 4]), u4 = *reinterpret_cast<const float4*>(&ss[x][tx * 4]);
+            const float a[4] = {a4.x, a4.y, a4.z, a4.w}, u[4] = {u4.x, u4.y, u4.z, u4.w};
+#pragma unroll
+            for (int i = 0; i < 4; ++i)
+#pragma unroll
+                for (int l = 0; l < 4; ++l) o2[i][l] = fmaf(a[i], u[l], o2[i][l]);
+        }
+    }
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const int t = ty * 4 + i;
+        if (t >= nt) continue;
+        float den = 1.0f;
+        if (C.gating == 1) {
+            float nq = sC[t] * sN[t];
+            for (int j = 0; j <= t; ++j) nq += pw[j][t];
+            den = fmaxf(fabsf(nq), expf(-sM[t])) + 1e-6f;
+        }
+#pragma unroll
+        for (int l = 0; l < 4; ++l) {
+            const int cv = cv0 + tx * 4 + l;
+            if (cv < dv) A.out[(int64_t)(tf + t) * H * dv + h * dv + cv] = fmaf(sC[t], o2[i][l], o1[i][l]) / den;
+        }
+    }
+}
+
 template <int kR, bool kExp>
 void launch_linear_attention(const LinAttnArgs& A, int num_seqs, bool single_rows, cudaStream_t st) {
     if (single_rows) {
@@ -743,6 +1107,52 @@ void linear_attention(const float* proj, int64_t ld, int32_t off_q, int32_t off_
     else dispatch_linear_attention<true>(A, num_seqs, single_rows != 0, st);
     count_launch();
     check_launch("linear_attention");
+}
+
+int64_t linear_attention_chunked_scratch(int32_t num_tokens, int32_t num_seqs, int32_t num_heads, int32_t dk, int32_t dv) {
+    // floats: per chunk slot a [dv, dk] term per head and two normaliser rows, per token three gate values per head, per entry a maximum per head
+    const int64_t slots = (int64_t)(num_tokens + kChunk - 1) / kChunk + num_seqs;
+    return slots * num_heads * ((int64_t)dv * dk + 2 * dk) + (int64_t)num_tokens * num_heads * 3 + (int64_t)num_seqs * num_heads;
+}
+
+
+void linear_attention_chunked(const float* proj, int64_t ld, int32_t off_q, int32_t off_k, int32_t off_v, int32_t off_i, int32_t off_f, const float* decay,
+                              const float* i_bias, const float* f_bias, float gate_cap, float q_scale, int32_t act, int32_t gating, float* state, float* normaliser,
+                              float* maximum, float* out, float* scratch, const int32_t* cu_seqlens, const int32_t* seq_slots, const int32_t* seq_start,
+                              int32_t num_tokens, int32_t num_seqs, int32_t max_rows, int32_t num_heads, int32_t dk, int32_t dv, int64_t stream) {
+    if (num_seqs == 0 || num_tokens == 0) return;
+    B200_REQUIRE(proj && state && out && scratch && cu_seqlens && seq_slots && seq_start && num_heads > 0 && num_heads <= 65535 && dk > 0 && dv > 0 && max_rows > 0 &&
+                 (act == 0 || act == 1) && (gating == 0 || gating == 1), kErrBadArg, "linear_attention_chunked: bad arguments");
+    B200_REQUIRE(gating == 0 ? decay != nullptr : (normaliser && maximum && gate_cap > 0.f), kErrBadArg,
+                 "linear_attention_chunked: fixed decay needs decay[H]; exponential gating needs the normaliser, the maximum and a positive cap");
+    const int max_chunks = (max_rows + kChunk - 1) / kChunk;
+    B200_REQUIRE((int64_t)max_chunks * num_seqs <= 65535, kErrUnsupported, "linear_attention_chunked: %d chunks x %d entries exceed the grid", max_chunks, num_seqs);
+    const int64_t slots = (int64_t)(num_tokens + kChunk - 1) / kChunk + num_seqs;
+    ChunkArgs C;
+    C.A = LinAttnArgs{proj, ld, off_q, off_k, off_v, off_i, off_f, decay, i_bias, f_bias, gate_cap, q_scale, act, state, normaliser, maximum, out,
+                      cu_seqlens, seq_slots, seq_start, num_heads, dk, dv};
+    C.U = scratch;
+    C.un = C.U + slots * num_heads * dv * dk;
+    C.un_in = C.un + slots * num_heads * dk;
+    C.gc = C.un_in + slots * num_heads * dk;
+    C.m0 = C.gc + (int64_t)num_tokens * num_heads * 3;
+    C.max_chunks = max_chunks;
+    C.gating = gating;
+    cudaStream_t st = as_stream(stream);
+    int launches = 3;
+    if (gating == 1) {
+        launch_pdl(la_gate_values_kernel, dim3(ceil_div((int64_t)num_tokens * num_heads, 256)), dim3(256), 0, st, C, (int)num_tokens);
+        launch_pdl(la_gate_chain_kernel, dim3(ceil_div(num_heads, 32), num_seqs), dim3(32), 0, st, C);
+        launches += 2;
+    }
+    const unsigned z = (unsigned)(max_chunks * num_seqs);
+    launch_pdl(la_chunk_state_kernel, dim3(ceil_div(dv, 64) * ceil_div(dk, 64), num_heads, z), dim3(256), 0, st, C);
+    launch_pdl(la_chunk_scan_kernel, dim3(ceil_div((int64_t)num_heads * dv * dk, 256), num_seqs), dim3(256), 0, st, C);
+    const int smem = (2 * 32 * 68 + 2 * 64 * 68 + 5 * 64) * (int)sizeof(float);
+    ensure_dynamic_smem(reinterpret_cast<const void*>(la_chunk_output_kernel), smem);
+    launch_pdl(la_chunk_output_kernel, dim3(ceil_div(dv, 64), num_heads, z), dim3(256), (size_t)smem, st, C);
+    count_launch(launches);
+    check_launch("linear_attention_chunked");
 }
 
 }  // extern "C"

@@ -394,6 +394,7 @@ class DecayLinearAttention:
         self.w_in = torch.cat([w["q"], w["k"], w["v"], w["g"]], 0).to(dtype).contiguous()
         self.off_g = 2 * heads * dk + heads * dv
         self.decay = torch.tensor([float(d) for d in decay], dtype=torch.float32, device=self.w_in.device)
+        self.kernel = None                       # None: chosen by the step's shape (tests force one)
         self.norm = w["norm"].float().contiguous()
         self.w_o = w["o"].to(dtype).contiguous()
 
@@ -403,7 +404,8 @@ class DecayLinearAttention:
     def forward(self, h: torch.Tensor, batch: StepBatch, cache, proj: Optional[torch.Tensor] = None) -> torch.Tensor:
         if proj is None:
             proj = ops.linear(h, self.w_in)
-        o = ops.linear_attention(proj, 0, self.H * self.dk, 2 * self.H * self.dk, cache[0], batch, self.H, self.dk, self.dv, act="silu", decay=self.decay)
+        o = ops.linear_attention(proj, 0, self.H * self.dk, 2 * self.H * self.dk, cache[0], batch, self.H, self.dk, self.dv, act="silu", decay=self.decay,
+                                 kernel=self.kernel)
         z = ops.group_rms_norm_gate(o, self.norm, proj[:, self.off_g:], 1, self.eps, self.dtype)
         return ops.linear(z, self.w_o)
 
@@ -420,6 +422,7 @@ class MatrixMemoryMixer:
         self.off_g = 2 * heads * dk + heads * dv
         self.off_i = self.off_g + heads * dv
         self.off_f = self.off_i + heads
+        self.kernel = None                       # None: chosen by the step's shape (tests force one)
         self.i_bias = w["i.b"].float().contiguous() if "i.b" in w else None
         self.f_bias = w["f.b"].float().contiguous() if "f.b" in w else None
         self.norm = w["norm"].float().contiguous()
@@ -434,7 +437,8 @@ class MatrixMemoryMixer:
         if proj is None:
             proj = ops.linear(h, self.w_in)
         gates = dict(off_i=self.off_i, off_f=self.off_f, i_bias=self.i_bias, f_bias=self.f_bias, cap=self.cap, normaliser=n, maximum=m)
-        o = ops.linear_attention(proj, 0, self.H * self.dk, 2 * self.H * self.dk, S, batch, self.H, self.dk, self.dv, q_scale=self.dk ** -0.5, gates=gates)
+        o = ops.linear_attention(proj, 0, self.H * self.dk, 2 * self.H * self.dk, S, batch, self.H, self.dk, self.dv, q_scale=self.dk ** -0.5, gates=gates,
+                                 kernel=self.kernel)
         z = ops.group_rms_norm_gate(o, self.norm, proj[:, self.off_g:], self.H, self.eps, self.dtype)
         return ops.linear(z, self.w_o)
 

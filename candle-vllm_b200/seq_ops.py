@@ -634,21 +634,46 @@ def gated_linear_scan(u: torch.Tensor, gates: torch.Tensor, lam: torch.Tensor, y
     return out
 
 
+CHUNKED_LINEAR_ATTENTION_MIN_ROWS = 64          # steps in which some entry brings at least this many rows take the chunked form
+CHUNKED_LINEAR_ATTENTION_SCRATCH = 1 << 30      # bytes of scratch above which a step stays on the token-by-token kernel
+
+
 def linear_attention(proj: torch.Tensor, off_q: int, off_k: int, off_v: int, state: torch.Tensor, batch: StepBatch, heads: int, dk: int, dv: int, act: str = "none",
-                     q_scale: float = 1.0, decay: Optional[torch.Tensor] = None, gates: Optional[dict] = None) -> torch.Tensor:
+                     q_scale: float = 1.0, decay: Optional[torch.Tensor] = None, gates: Optional[dict] = None, kernel: Optional[str] = None) -> torch.Tensor:
     """S <- a S + b k v^T, o = S^T q per head on columns of ``proj`` (f32 [T, ld]); state f32 [slots, H, dv, dk] advanced in place.  ``decay`` f32 [H]: a fixed
     decay per head.  ``gates`` = dict(off_i, off_f, i_bias, f_bias, cap, normaliser, maximum): exponential gating with a running maximum and a normaliser
-    (states [slots, H, ceil(dv / 16), dk] and [slots, H, ceil(dv / 16)]).  -> f32 [T, H dv]"""
+    (states [slots, H, ceil(dv / 16), dk] and [slots, H, ceil(dv / 16)]).  -> f32 [T, H dv].  Three kernels compute the same rule: "step" (every entry brings
+    one token), "token" (token by token in tiles of 16, any step) and "chunked" (over chunks of 64 tokens, all chunks at once, for portions of prompts);
+    ``kernel`` forces one, None chooses by the step's shape."""
     T = proj.shape[0]
     out = torch.empty((T, heads * dv), dtype=torch.float32, device=proj.device)
     if (decay is None) == (gates is None):
         raise BackendError("linear_attention: either a fixed decay or exponential gates")
     g = gates or {}
+    if kernel is None:
+        kernel = "step" if batch.pure_decode else "token"
+        if batch.max_rows >= CHUNKED_LINEAR_ATTENTION_MIN_ROWS and -(-batch.max_rows // 64) * batch.num_seqs <= 65535:
+            need = int(lib().linear_attention_chunked_scratch(C.c_int32(T), C.c_int32(batch.num_seqs), C.c_int32(heads), C.c_int32(dk), C.c_int32(dv)))
+            if need * 4 <= CHUNKED_LINEAR_ATTENTION_SCRATCH:
+                kernel = "chunked"
+    if kernel == "chunked":
+        need = int(lib().linear_attention_chunked_scratch(C.c_int32(T), C.c_int32(batch.num_seqs), C.c_int32(heads), C.c_int32(dk), C.c_int32(dv)))
+        scratch = torch.empty((need,), dtype=torch.float32, device=proj.device)
+        lib().linear_attention_chunked(_ptr(proj), C.c_int64(proj.stride(0) if T > 1 else proj.shape[1]), C.c_int32(off_q), C.c_int32(off_k), C.c_int32(off_v),
+                                       C.c_int32(g.get("off_i", 0)), C.c_int32(g.get("off_f", 0)), _ptr(decay), _ptr(g.get("i_bias")), _ptr(g.get("f_bias")),
+                                       C.c_float(g.get("cap", 0.0)), C.c_float(q_scale), C.c_int32({"none": 0, "silu": 1}[act]), C.c_int32(0 if gates is None else 1),
+                                       _ptr(state), _ptr(g.get("normaliser")), _ptr(g.get("maximum")), _ptr(out), _ptr(scratch), _ptr(batch.cu_seqlens),
+                                       _ptr(batch.seq_slots), _ptr(batch.seq_start), C.c_int32(T), C.c_int32(batch.num_seqs), C.c_int32(batch.max_rows), C.c_int32(heads),
+                                       C.c_int32(dk), C.c_int32(dv), _stream(proj.device))
+        check("linear_attention_chunked")
+        return out
+    if kernel not in ("step", "token"):
+        raise BackendError(f"linear_attention: unknown kernel {kernel!r}")
     lib().linear_attention(_ptr(proj), C.c_int64(proj.stride(0) if T > 1 else proj.shape[1]), C.c_int32(off_q), C.c_int32(off_k), C.c_int32(off_v),
                            C.c_int32(g.get("off_i", 0)), C.c_int32(g.get("off_f", 0)), _ptr(decay), _ptr(g.get("i_bias")), _ptr(g.get("f_bias")),
                            C.c_float(g.get("cap", 0.0)), C.c_float(q_scale), C.c_int32({"none": 0, "silu": 1}[act]), C.c_int32(0 if gates is None else 1), _ptr(state),
                            _ptr(g.get("normaliser")), _ptr(g.get("maximum")), _ptr(out), _ptr(batch.cu_seqlens), _ptr(batch.seq_slots), _ptr(batch.seq_start),
-                           C.c_int32(T), C.c_int32(batch.num_seqs), C.c_int32(1 if batch.pure_decode else 0), C.c_int32(heads), C.c_int32(dk), C.c_int32(dv),
+                           C.c_int32(T), C.c_int32(batch.num_seqs), C.c_int32(1 if kernel == "step" else 0), C.c_int32(heads), C.c_int32(dk), C.c_int32(dv),
                            _stream(proj.device))
     check("linear_attention")
     return out

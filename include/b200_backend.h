@@ -592,6 +592,9 @@ void moe_down(const void* act, const void* w_down, const int32_t* ids, const int
  *   start) m' = max(f + m, i): a = e^(f + m - m'), b = e^(i - m'), normaliser n <- a n + b k, o = S^T q / (max(|n . q|, e^(-m')) + 1e-6);
  *   normaliser f32 [slots, H, ceil(dv / 16), dk] and maximum f32 [slots, H, ceil(dv / 16)] (one copy per block of 16 value columns).  out f32
  *   [T, H dv].  dk <= 256.  single_rows != 0 (every entry brings exactly one row): a kernel that stages nothing and takes one pass over the state.
+ * linear_attention_chunked: the same rule and arguments for steps with portions of prompts, evaluated over chunks of 64 tokens, all chunks at once (a [dv, dk]
+ *   product per chunk, a walk over every entry's chunks per state element, then scores, values and entering state per chunk); results differ from
+ *   linear_attention by rounding only.  max_rows = the most rows any entry brings; scratch = linear_attention_chunked_scratch(...) floats.
  * qk_norm_rope_cache_ex: qk_norm_rope_cache plus a query temperature (q times 1 + q_temp_coef ln(floor((p + 1) / q_temp_every) + 1); every 0 = off)
  *   and, with v_unit_rms, values divided by their root mean square per head (eps inside the root) before they are cached.
  * moe_route_ex: moe_route with score_fn 0 = softmax, 1 = sigmoid per output, and normalise 0 = the chosen scores times scale as they are.
@@ -623,6 +626,11 @@ void linear_attention(const float* proj, int64_t ld, int32_t off_q, int32_t off_
                       const float* i_bias, const float* f_bias, float gate_cap, float q_scale, int32_t act, int32_t gating, float* state, float* normaliser,
                       float* maximum, float* out, const int32_t* cu_seqlens, const int32_t* seq_slots, const int32_t* seq_start, int32_t num_tokens,
                       int32_t num_seqs, int32_t single_rows, int32_t num_heads, int32_t dk, int32_t dv, int64_t stream);
+int64_t linear_attention_chunked_scratch(int32_t num_tokens, int32_t num_seqs, int32_t num_heads, int32_t dk, int32_t dv);
+void linear_attention_chunked(const float* proj, int64_t ld, int32_t off_q, int32_t off_k, int32_t off_v, int32_t off_i, int32_t off_f, const float* decay,
+                              const float* i_bias, const float* f_bias, float gate_cap, float q_scale, int32_t act, int32_t gating, float* state, float* normaliser,
+                              float* maximum, float* out, float* scratch, const int32_t* cu_seqlens, const int32_t* seq_slots, const int32_t* seq_start,
+                              int32_t num_tokens, int32_t num_seqs, int32_t max_rows, int32_t num_heads, int32_t dk, int32_t dv, int64_t stream);
 void qk_norm_rope_cache_ex(const float* qkv, int64_t ld, const float* q_norm_w, const float* k_norm_w, const float* cos_t, const float* sin_t,
                            int32_t max_pos, const int32_t* positions, const int64_t* slot_mapping, void* q_out, void* key_cache, void* value_cache,
                            int32_t num_tokens, int32_t num_heads, int32_t num_kv_heads, int32_t dk, int32_t dv, int32_t rot_dims, float eps,

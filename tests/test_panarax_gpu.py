@@ -246,16 +246,18 @@ def _lightning_weights(D, H, dk, dv, seed, decay=None):
     return cfg["layers"][0]["mixer"]["decay"], {k[7:]: v.float() for k, v in S.panarax_weights(cfg, seed).items() if k.startswith("l0.mix.")}
 
 
+@pytest.mark.parametrize("kernel", ["token", "chunked", None])
 @pytest.mark.parametrize("H,dk,dv", [(3, 12, 20), (2, 64, 64), (2, 100, 40), (1, 256, 16), (4, 32, 130), (2, 30, 17)])
 @pytest.mark.parametrize("sizes", SIZES)
-def test_decay_linear_attention(H, dk, dv, sizes):
-    D, T = 24, 70
+def test_decay_linear_attention(H, dk, dv, sizes, kernel):
+    D, T = 24, 150
     decay, w = _lightning_weights(D, H, dk, dv, dk + dv)
     h = torch.randn(T, D, generator=torch.Generator().manual_seed(dk))
     want = P.lightning_mixer(h.to(F64), {k: v.to(F64) for k, v in w.items()}, H, dk, dv, decay, 1e-6)
     mix = M.DecayLinearAttention({k: v.to(DEV) for k, v in w.items()}, H, dk, dv, decay, 1e-6, torch.float32)
+    mix.kernel = kernel
     state, hd = tuple(dirty(s) for s in mix.state_shapes()), dev(h)
-    close(feed(lambda b, lo, hi: mix.forward(hd[lo:hi], b, state), T, sizes), want, 2e-5, f"fixed decay, portions {sizes}")
+    close(feed(lambda b, lo, hi: mix.forward(hd[lo:hi], b, state), T, sizes), want, 2e-5, f"fixed decay, portions {sizes}, kernel {kernel}")
 
 
 def test_decay_attention_keeps_a_far_key():
@@ -279,16 +281,18 @@ def _memory_weights(D, H, dk, dv, seed, cap=12.0):
     return {k[13:]: v.float() for k, v in S.panarax_weights(cfg, seed).items() if k.startswith("l0.mix.right.") and k != "l0.mix.right.out"}
 
 
+@pytest.mark.parametrize("kernel", ["token", "chunked", None])
 @pytest.mark.parametrize("H,dk,dv", [(3, 10, 18), (2, 64, 64), (2, 100, 40), (1, 256, 16), (4, 32, 130), (2, 30, 17)])
 @pytest.mark.parametrize("sizes", SIZES)
-def test_matrix_memory(H, dk, dv, sizes):
-    D, T = 24, 70
+def test_matrix_memory(H, dk, dv, sizes, kernel):
+    D, T = 24, 150
     w = _memory_weights(D, H, dk, dv, dk + dv)
     h = torch.randn(T, D, generator=torch.Generator().manual_seed(dv))
     want = P.matrix_memory(h.to(F64), {k: v.to(F64) for k, v in w.items()}, H, dk, dv, 12.0, 1e-6)
     mix = M.MatrixMemoryMixer({k: v.to(DEV) for k, v in w.items()}, H, dk, dv, 12.0, 1e-6, torch.float32)
+    mix.kernel = kernel
     state, hd = tuple(dirty(s) for s in mix.state_shapes()), dev(h)
-    close(feed(lambda b, lo, hi: mix.forward(hd[lo:hi], b, state), T, sizes), want, 5e-5, f"matrix memory, portions {sizes}")
+    close(feed(lambda b, lo, hi: mix.forward(hd[lo:hi], b, state), T, sizes), want, 5e-5, f"matrix memory, portions {sizes}, kernel {kernel}")
 
 
 @pytest.mark.parametrize("case", ["capped", "closed", "open"])
@@ -306,21 +310,25 @@ def test_matrix_memory_gates(case):
     h = torch.randn(T, D, generator=torch.Generator().manual_seed(2))
     want = P.matrix_memory(h.to(F64), {k: v.to(F64) for k, v in w.items()}, H, dk, dv, cap, 1e-6)
     mix = M.MatrixMemoryMixer({k: v.to(DEV) for k, v in w.items()}, H, dk, dv, cap, 1e-6, torch.float32)
-    for sizes in ([130], [1], [17, 2, 1]):
-        state, hd = tuple(dirty(s) for s in mix.state_shapes()), dev(h)
-        close(feed(lambda b, lo, hi: mix.forward(hd[lo:hi], b, state), T, sizes), want, 1e-4, f"{case} gates, portions {sizes}")
+    for kernel in ("token", "chunked"):
+        mix.kernel = kernel
+        for sizes in ([130], [1], [17, 2, 1], [70, 3, 57]):
+            state, hd = tuple(dirty(s) for s in mix.state_shapes()), dev(h)
+            close(feed(lambda b, lo, hi: mix.forward(hd[lo:hi], b, state), T, sizes), want, 1e-4, f"{case} gates, portions {sizes}, kernel {kernel}")
 
 
-def test_linear_attention_unequal_entries():
+@pytest.mark.parametrize("kernel", ["token", "chunked"])
+def test_linear_attention_unequal_entries(kernel):
     D, H, dk, dv = 24, 3, 20, 36
     w = _memory_weights(D, H, dk, dv, 5)
     g = torch.Generator().manual_seed(6)
-    lens = [33, 1, 2, 50]
+    lens = [133, 1, 2, 150]
     hs = [torch.randn(n, D, generator=g) for n in lens]
     wants = [P.matrix_memory(h.to(F64), {k: v.to(F64) for k, v in w.items()}, H, dk, dv, 12.0, 1e-6) for h in hs]
     mix = M.MatrixMemoryMixer({k: v.to(DEV) for k, v in w.items()}, H, dk, dv, 12.0, 1e-6, torch.float32)
+    mix.kernel = kernel
     state = tuple(dirty(s, slots=4) for s in mix.state_shapes())
-    cut = [16, 1, 1, 17]
+    cut = [66, 1, 1, 17]
     a = mix.forward(dev(torch.cat([h[:c] for h, c in zip(hs, cut)])), step([(0, c, 3 - i) for i, c in enumerate(cut)]), state)
     rest = [(i, lens[i] - cut[i]) for i in (2, 3, 0)]
     b = mix.forward(dev(torch.cat([hs[i][cut[i]:] for i, _ in rest])), step([(cut[i], n, 3 - i) for i, n in rest]), state)
