@@ -269,17 +269,31 @@ group_rms_norm_gate_kernel(const float* __restrict__ o, int64_t ldo, const float
 
 
 template <typename TS, typename TOut>
-__global__ void head_gate_kernel(const TS* __restrict__ src, const float* __restrict__ gate, int64_t ldg, TOut* __restrict__ out, int64_t rows, int H, int dv) {
+__global__ void head_gate_kernel(const TS* __restrict__ src, const float* __restrict__ gate, int64_t ldg, TOut* __restrict__ out, int H, int dv) {
     pdl_wait();
     pdl_trigger();
-    const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
-    const int64_t n = (int64_t)H * dv;
-    if (i >= rows * n) return;
-    const int64_t r = i / n;
-    const int h = (int)((i - r * n) / dv);
-    out[i] = from_f32<TOut>(to_f32<TS>(src[i]) / (1.0f + expf(-gate[r * ldg + h])));
+    // a thread takes four neighbours of one row (of one head when dv is a multiple of four)
+    const int64_t r = blockIdx.y;
+    const int n = H * dv;
+    const int i0 = (blockIdx.x * blockDim.x + threadIdx.x) * 4;
+    if (i0 >= n) return;
+    const TS* sp = src + r * n;
+    TOut* op = out + r * n;
+    if ((dv & 3) == 0) {
+        const float g = 1.0f / (1.0f + expf(-gate[r * ldg + i0 / dv]));
+        float v[4];
+        if (sizeof(TS) == 4) { const float4 t = *reinterpret_cast<const float4*>(sp + i0); v[0] = t.x; v[1] = t.y; v[2] = t.z; v[3] = t.w; }
+        else { const uint2 t = *reinterpret_cast<const uint2*>(sp + i0); const TS* e = reinterpret_cast<const TS*>(&t); for (int j = 0; j < 4; ++j) v[j] = to_f32<TS>(e[j]); }
+        if (sizeof(TOut) == 4) *reinterpret_cast<float4*>(op + i0) = make_float4(v[0] * g, v[1] * g, v[2] * g, v[3] * g);
+        else {
+            TOut o[4];
+            for (int j = 0; j < 4; ++j) o[j] = from_f32<TOut>(v[j] * g);
+            *reinterpret_cast<uint2*>(op + i0) = *reinterpret_cast<const uint2*>(o);
+        }
+        return;
+    }
+    for (int i = i0; i < min(i0 + 4, n); ++i) op[i] = from_f32<TOut>(to_f32<TS>(sp[i]) / (1.0f + expf(-gate[r * ldg + i / dv])));
 }
-
 
 // the closing sum of one sublayer and the opening norm of the next in one pass over the row: x <- x + sigmoid(z + zb) * y, then the layer norm of the new x
 template <typename TOut>
@@ -476,10 +490,10 @@ void head_gate(const void* src, int32_t src_dtype, const float* gate, int64_t ld
                int64_t stream) {
     if (num_tokens == 0) return;
     B200_REQUIRE(src && gate && out && num_heads > 0 && dv > 0 && ld_gate >= num_heads, kErrBadArg, "head_gate: bad arguments");
-    const int64_t total = (int64_t)num_tokens * num_heads * dv;
-    const unsigned grid = (unsigned)((total + 255) / 256);
+    B200_REQUIRE(num_tokens <= 65535, kErrUnsupported, "head_gate: at most 65535 rows per call");
+    const dim3 grid((unsigned)(((int64_t)num_heads * dv + 1023) / 1024), (unsigned)num_tokens);
     cudaStream_t st = as_stream(stream);
-#define HG(TS, TO) launch_pdl(head_gate_kernel<TS, TO>, dim3(grid), dim3(256), 0, st, (const TS*)src, gate, ld_gate, (TO*)out, (int64_t)num_tokens, num_heads, dv)
+#define HG(TS, TO) launch_pdl(head_gate_kernel<TS, TO>, grid, dim3(256), 0, st, (const TS*)src, gate, ld_gate, (TO*)out, num_heads, dv)
     if (src_dtype == B200_F32 && out_dtype == B200_F32) HG(float, float);
     else if (src_dtype == B200_F32 && out_dtype == B200_BF16) HG(float, __nv_bfloat16);
     else if (src_dtype == B200_BF16 && out_dtype == B200_BF16) HG(__nv_bfloat16, __nv_bfloat16);

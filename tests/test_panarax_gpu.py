@@ -136,6 +136,17 @@ def test_gated_residual_and_gated_units():
     close(ops.glu_packed(dev(gu), "clamped", torch.float32, lim, row_scale=dev(sc), scale_index=idx.to(DEV)), want, 2e-6, "clamped, scaled rows")
 
 
+@pytest.mark.parametrize("H,dv", [(3, 20), (5, 7), (2, 128)])
+def test_head_gate(H, dv):
+    g = torch.Generator().manual_seed(dv)
+    a, z = torch.randn(9, H * dv, generator=g) * 2, torch.randn(9, H + 3, generator=g)
+    want = (a.to(F64).view(9, H, dv) * torch.sigmoid(z[:, 3:].to(F64)).unsqueeze(-1)).reshape(9, H * dv)
+    close(ops.head_gate(dev(a), dev(z)[:, 3:], H, dv, torch.float32), want, 2e-6, "f32 -> f32")
+    close(ops.head_gate(dev(a), dev(z)[:, 3:], H, dv, BF), want, 6e-3, "f32 -> bf16")
+    close(ops.head_gate(dev(a, BF), dev(z)[:, 3:], H, dv, BF), (bf_round(a).to(F64).view(9, H, dv) * torch.sigmoid(z[:, 3:].to(F64)).unsqueeze(-1)).reshape(9, H * dv),
+          6e-3, "bf16 -> bf16")
+
+
 @pytest.mark.parametrize("groups,gate_act", [(1, "sigmoid"), (3, "sigmoid"), (6, "silu")])
 def test_group_norm_with_gate(groups, gate_act):
     g = torch.Generator().manual_seed(2)
