@@ -989,6 +989,7 @@ bool dispatch_linear_attention(const LinAttnArgs& A, int num_seqs, bool single_r
     else if (A.dk <= 64) launch_linear_attention<8, kExp>(A, num_seqs, single_rows, st);
     else if (A.dk <= 128) launch_linear_attention<16, kExp>(A, num_seqs, single_rows, st);
     else if (A.dk <= 256) launch_linear_attention<32, kExp>(A, num_seqs, single_rows, st);
+    else if (A.dk <= 512) launch_linear_attention<64, kExp>(A, num_seqs, single_rows, st);      // spills its staging registers: a path for correctness, not speed
     else return false;
     return true;
 }
@@ -1099,7 +1100,7 @@ void linear_attention(const float* proj, int64_t ld, int32_t off_q, int32_t off_
                  (act == 0 || act == 1) && (gating == 0 || gating == 1), kErrBadArg, "linear_attention: bad arguments");
     B200_REQUIRE(gating == 0 ? decay != nullptr : (normaliser && maximum && gate_cap > 0.f), kErrBadArg,
                  "linear_attention: fixed decay needs decay[H]; exponential gating needs the normaliser, the maximum and a positive cap");
-    B200_REQUIRE(dk <= 256, kErrUnsupported, "linear_attention: key size %d > 256", dk);
+    B200_REQUIRE(dk <= 512, kErrUnsupported, "linear_attention: key size %d > 512", dk);
     LinAttnArgs A{proj, ld, off_q, off_k, off_v, off_i, off_f, decay, i_bias, f_bias, gate_cap, q_scale, act, state, normaliser, maximum, out,
                   cu_seqlens, seq_slots, seq_start, num_heads, dk, dv};
     cudaStream_t st = as_stream(stream);

@@ -591,7 +591,7 @@ void moe_down(const void* act, const void* w_down, const int32_t* ids, const int
  *   tanh((proj[off_i + h] + i_bias[h]) / cap), f = logsigmoid(cap tanh((proj[off_f + h] + f_bias[h]) / cap)) and the running maximum m (0 at the
  *   start) m' = max(f + m, i): a = e^(f + m - m'), b = e^(i - m'), normaliser n <- a n + b k, o = S^T q / (max(|n . q|, e^(-m')) + 1e-6);
  *   normaliser f32 [slots, H, ceil(dv / 16), dk] and maximum f32 [slots, H, ceil(dv / 16)] (one copy per block of 16 value columns).  out f32
- *   [T, H dv].  dk <= 256.  single_rows != 0 (every entry brings exactly one row): a kernel that stages nothing and takes one pass over the state.
+ *   [T, H dv].  dk <= 512.  single_rows != 0 (every entry brings exactly one row): a kernel that stages nothing and takes one pass over the state.
  * linear_attention_chunked: the same rule and arguments for steps with portions of prompts, evaluated over chunks of 64 tokens, all chunks at once (a [dv, dk]
  *   product per chunk, a walk over every entry's chunks per state element, then scores, values and entering state per chunk); results differ from
  *   linear_attention by rounding only.  max_rows = the most rows any entry brings; scratch = linear_attention_chunked_scratch(...) floats.

@@ -258,7 +258,7 @@ def _lightning_weights(D, H, dk, dv, seed, decay=None):
 
 
 @pytest.mark.parametrize("kernel", ["token", "chunked", None])
-@pytest.mark.parametrize("H,dk,dv", [(3, 12, 20), (2, 64, 64), (2, 100, 40), (1, 256, 16), (4, 32, 130), (2, 30, 17)])
+@pytest.mark.parametrize("H,dk,dv", [(3, 12, 20), (2, 64, 64), (2, 100, 40), (1, 256, 16), (4, 32, 130), (2, 30, 17), (1, 300, 8)])
 @pytest.mark.parametrize("sizes", SIZES)
 def test_decay_linear_attention(H, dk, dv, sizes, kernel):
     D, T = 24, 150
@@ -293,7 +293,7 @@ def _memory_weights(D, H, dk, dv, seed, cap=12.0):
 
 
 @pytest.mark.parametrize("kernel", ["token", "chunked", None])
-@pytest.mark.parametrize("H,dk,dv", [(3, 10, 18), (2, 64, 64), (2, 100, 40), (1, 256, 16), (4, 32, 130), (2, 30, 17)])
+@pytest.mark.parametrize("H,dk,dv", [(3, 10, 18), (2, 64, 64), (2, 100, 40), (1, 256, 16), (4, 32, 130), (2, 30, 17), (1, 300, 8)])
 @pytest.mark.parametrize("sizes", SIZES)
 def test_matrix_memory(H, dk, dv, sizes, kernel):
     D, T = 24, 150
