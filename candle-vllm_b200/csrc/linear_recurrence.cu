@@ -9,7 +9,8 @@
 //                         channels, true 32-bit products (the gates of a recurrence).
 //   gated_linear_scan     per channel  S_t = a_t S_(t-1) + sqrt(1 - a_t^2) i_t u_t,  a_t = exp(-c r_t softplus(lam)),  r, i = sigmoid of
 //                         the block-diagonal products;  out_t = S_t * gelu_tanh(y_t + y_bias).  One kernel for steps of few rows per entry;
-//                         for portions of prompts a row-parallel pass first turns gates and y into a_t, the input term and the GELU (in place).
+//                         for portions of prompts a row-parallel pass first turns gates and y into a_t, the input term and the GELU (in place);
+//                         from 512 rows per entry the bare scan that follows runs over chunks of 128 rows, all chunks at once.
 //   linear_attention      per head, S [dk, dv]:  S_t = a_t S_(t-1) + b_t k_t v_t^T,  o_t = S_t^T q_t, in two gatings:
 //                           fixed decay      a = decay[h], b = 1;
 //                           exponential      a_t = e^(f_t + m_(t-1) - m_t), b_t = e^(i_t - m_t) with the running maximum m_t = max(f_t + m_(t-1), i_t),
@@ -309,8 +310,98 @@ linear_scan_kernel(const float* __restrict__ gates, int64_t ldg, const float* __
     *sp = S;
 }
 
+// Long portions: the bare scan cut into chunks of 128 rows, all chunks at once.  A chunk's rows compose to S_out = P S_in + Q with P the product of
+// its a_t and Q its own scan from zero: one kernel takes (P, Q) of every chunk, one walks an entry's chunks per channel and leaves every chunk's S_in,
+// one replays every chunk from its S_in and writes the outputs.  The association of the sums differs from the row-by-row scan by rounding only.
+constexpr int kScanChunk = 128;
+
+__device__ __forceinline__ int scan_chunk_base(const int32_t* cu, int b) {
+    int s = 0;
+    for (int i = 0; i < b; ++i) s += (cu[i + 1] - cu[i] + kScanChunk - 1) / kScanChunk;
+    return s;
+}
+
+__global__ void __launch_bounds__(128)
+scan_chunk_compose_kernel(const float* __restrict__ gates, int64_t ldg, float* __restrict__ pq, const int32_t* __restrict__ cu_seqlens, int C, int n) {
+    pdl_wait();
+    pdl_trigger();
+    const int c = blockIdx.x * 128 + threadIdx.x, ch = blockIdx.y, b = blockIdx.z;
+    if (c >= C) return;
+    const int t0 = cu_seqlens[b], rows = cu_seqlens[b + 1] - t0;
+    if (ch * kScanChunk >= rows) return;
+    const int tf = t0 + ch * kScanChunk, nt = min(kScanChunk, rows - ch * kScanChunk);
+    const int blk = c / n, j = c - blk * n;
+    const float* ga = gates + (int64_t)tf * ldg + blk * 2 * n + j;
+    float P = 1.f, Q = 0.f;
+#pragma unroll 8
+    for (int t = 0; t < nt; ++t) {
+        const float a = ga[(int64_t)t * ldg], bb = ga[(int64_t)t * ldg + n];
+        Q = fmaf(a, Q, bb);
+        P *= a;
+    }
+    const int64_t at = ((int64_t)(scan_chunk_base(cu_seqlens, b) + ch) * C + c) * 2;
+    pq[at] = P; pq[at + 1] = Q;
+}
+
+__global__ void __launch_bounds__(128)
+scan_chunk_carry_kernel(float* __restrict__ pq, float* __restrict__ state, const int32_t* __restrict__ cu_seqlens, const int32_t* __restrict__ seq_slots,
+                        const int32_t* __restrict__ seq_start, int C) {
+    pdl_wait();
+    pdl_trigger();
+    const int c = blockIdx.x * 128 + threadIdx.x, b = blockIdx.y;
+    if (c >= C) return;
+    const int rows = cu_seqlens[b + 1] - cu_seqlens[b];
+    if (rows <= 0) return;
+    const int nc = (rows + kScanChunk - 1) / kScanChunk;
+    float* sp = state + (int64_t)seq_slots[b] * C + c;
+    float S = seq_start[b] == 0 ? 0.f : *sp;
+    float2* p0 = reinterpret_cast<float2*>(pq) + (int64_t)scan_chunk_base(cu_seqlens, b) * C + c;
+    constexpr int kAhead = 8;
+    float2 nx[kAhead];
+#pragma unroll
+    for (int a = 0; a < kAhead; ++a) nx[a] = p0[(int64_t)min(a, nc - 1) * C];
+    for (int cb = 0; cb < nc; cb += kAhead) {
+        float2 cur[kAhead];
+#pragma unroll
+        for (int a = 0; a < kAhead; ++a) cur[a] = nx[a];
+#pragma unroll
+        for (int a = 0; a < kAhead; ++a) nx[a] = p0[(int64_t)min(cb + kAhead + a, nc - 1) * C];
+#pragma unroll
+        for (int a = 0; a < kAhead; ++a) {
+            if (cb + a >= nc) break;
+            p0[(int64_t)(cb + a) * C].y = S;                 // the state that enters the chunk
+            S = fmaf(cur[a].x, S, cur[a].y);
+        }
+    }
+    *sp = S;
+}
+
+template <typename TOut>
+__global__ void __launch_bounds__(128)
+scan_chunk_replay_kernel(const float* __restrict__ gates, int64_t ldg, const float* __restrict__ y, int64_t ldy, const float* __restrict__ pq, TOut* __restrict__ out,
+                         const int32_t* __restrict__ cu_seqlens, int C, int n) {
+    pdl_wait();
+    pdl_trigger();
+    const int c = blockIdx.x * 128 + threadIdx.x, ch = blockIdx.y, b = blockIdx.z;
+    if (c >= C) return;
+    const int t0 = cu_seqlens[b], rows = cu_seqlens[b + 1] - t0;
+    if (ch * kScanChunk >= rows) return;
+    const int tf = t0 + ch * kScanChunk, nt = min(kScanChunk, rows - ch * kScanChunk);
+    const int blk = c / n, j = c - blk * n;
+    const float* ga = gates + (int64_t)tf * ldg + blk * 2 * n + j;
+    const float* yp = y + (int64_t)tf * ldy + c;
+    TOut* op = out + (int64_t)tf * C + c;
+    float S = pq[((int64_t)(scan_chunk_base(cu_seqlens, b) + ch) * C + c) * 2 + 1];
+#pragma unroll 8
+    for (int t = 0; t < nt; ++t) {
+        S = fmaf(ga[(int64_t)t * ldg], S, ga[(int64_t)t * ldg + n]);
+        op[(int64_t)t * C] = from_f32<TOut>(S * yp[(int64_t)t * ldy]);
+    }
+}
+
 // ---- linear attention with a matrix state ---------------------------------------------------------------------------------------------
 constexpr int kTile = 16;
+constexpr int kScanChunkedRows = 512;    // entries with at least this many rows (and a scratch buffer): the bare scan runs over chunks of 128 rows, all at once
 constexpr int kScanSplitRows = 16;     // entries with at least this many rows: the gated scan runs as a row-parallel pass plus a bare scan
 
 struct LinAttnArgs {
@@ -1055,7 +1146,7 @@ void block_diag_linear(const float* x, int64_t ldx, const float* weight, const f
 }
 
 void gated_linear_scan(const float* u, int64_t ldu, float* gates, int64_t ld_gates, const float* lam, float* y_pre, int64_t ldy, const float* y_bias,
-                       float* state, void* out, const int32_t* cu_seqlens, const int32_t* seq_slots, const int32_t* seq_start, int32_t num_tokens, int32_t num_seqs,
+                       float* state, void* out, float* scratch, const int32_t* cu_seqlens, const int32_t* seq_slots, const int32_t* seq_start, int32_t num_tokens, int32_t num_seqs,
                        int32_t max_rows, int32_t channels, int32_t block_channels, float decay_scale, int32_t out_dtype, int64_t stream) {
     if (num_seqs == 0 || num_tokens == 0) return;
     B200_REQUIRE(u && gates && lam && y_pre && state && out && cu_seqlens && seq_slots && seq_start && channels > 0 && block_channels > 0 &&
@@ -1068,6 +1159,21 @@ void gated_linear_scan(const float* u, int64_t ldu, float* gates, int64_t ld_gat
         const int64_t total = (int64_t)num_tokens * channels;
         launch_pdl(gated_scan_prepare_kernel, dim3((unsigned)((total + 255) / 256)), dim3(256), 0, st, u, ldu, gates, ld_gates, lam, y_pre, ldy, y_bias,
                    (int64_t)num_tokens, channels, block_channels, decay_scale);
+        if (max_rows >= kScanChunkedRows && scratch && (int64_t)ceil_div(max_rows, kScanChunk) * num_seqs <= 65535) {
+            const int max_chunks = ceil_div(max_rows, kScanChunk);
+            const dim3 cgrid(ceil_div(channels, 128), max_chunks, num_seqs);
+            launch_pdl(scan_chunk_compose_kernel, cgrid, dim3(128), 0, st, (const float*)gates, ld_gates, scratch, cu_seqlens, channels, block_channels);
+            launch_pdl(scan_chunk_carry_kernel, dim3(ceil_div(channels, 128), num_seqs), dim3(128), 0, st, scratch, state, cu_seqlens, seq_slots, seq_start, channels);
+            if (out_dtype == B200_F32)
+                launch_pdl(scan_chunk_replay_kernel<float>, cgrid, dim3(128), 0, st, (const float*)gates, ld_gates, (const float*)y_pre, ldy, (const float*)scratch,
+                           (float*)out, cu_seqlens, channels, block_channels);
+            else
+                launch_pdl(scan_chunk_replay_kernel<__nv_bfloat16>, cgrid, dim3(128), 0, st, (const float*)gates, ld_gates, (const float*)y_pre, ldy,
+                           (const float*)scratch, (__nv_bfloat16*)out, cu_seqlens, channels, block_channels);
+            count_launch(4);
+            check_launch("gated_linear_scan");
+            return;
+        }
         const dim3 grid(ceil_div(channels, 32), num_seqs);
         if (out_dtype == B200_F32)
             launch_pdl(linear_scan_kernel<float>, grid, dim3(32), 0, st, (const float*)gates, ld_gates, (const float*)y_pre, ldy, state, (float*)out, cu_seqlens, seq_slots,

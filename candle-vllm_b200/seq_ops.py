@@ -627,8 +627,10 @@ def gated_linear_scan(u: torch.Tensor, gates: torch.Tensor, lam: torch.Tensor, y
     T, Cn = u.shape
     out = torch.empty((T, Cn), dtype=out_dtype, device=u.device)
     pitch = lambda t, n: t.stride(0) if T > 1 else max(n, t.stride(0))
+    # long portions: room for a (product, partial scan) pair per chunk of 128 rows and channel
+    scratch = torch.empty((2 * Cn * (-(-T // 128) + batch.num_seqs),), dtype=torch.float32, device=u.device) if batch.max_rows >= 512 else None
     lib().gated_linear_scan(_ptr(u), C.c_int64(pitch(u, Cn)), _ptr(gates), C.c_int64(pitch(gates, 2 * Cn)), _ptr(lam), _ptr(y_pre), C.c_int64(pitch(y_pre, Cn)), _ptr(y_bias),
-                            _ptr(state), _ptr(out), _ptr(batch.cu_seqlens), _ptr(batch.seq_slots), _ptr(batch.seq_start), C.c_int32(T), C.c_int32(batch.num_seqs),
+                            _ptr(state), _ptr(out), _ptr(scratch), _ptr(batch.cu_seqlens), _ptr(batch.seq_slots), _ptr(batch.seq_start), C.c_int32(T), C.c_int32(batch.num_seqs),
                             C.c_int32(batch.max_rows), C.c_int32(Cn), C.c_int32(block_channels), C.c_float(decay_scale), C.c_int32(_tag(out_dtype)), _stream(u.device))
     check("gated_linear_scan")
     return out

@@ -585,7 +585,8 @@ void moe_down(const void* act, const void* w_down, const int32_t* ids, const int
  * gated_linear_scan: per channel c of block c / block_channels: r = sigmoid(gates[t, blk, j]), i = sigmoid(gates[t, blk, n + j]) (gates f32 [T, blocks,
  *   2 n], n = block_channels, j = c mod n); log a = -decay_scale r softplus(lam[c]); S <- a S + sqrt(1 - a^2) i u[t, c]; out[t, c] = S *
  *   gelu_tanh(y_pre[t, c] + y_bias[c]).  state f32 [slots, channels].  max_rows = the most rows any entry brings: from 16 on, the per-row part runs
- *   as a pass of its own that overwrites gates and y_pre with its results (both are scratch to the caller), and the scan is two multiply-adds per row.
+ *   as a pass of its own that overwrites gates and y_pre with its results (both are scratch to the caller), and the scan is two multiply-adds per row;
+ *   from 512 on, with scratch (f32, 2 * channels * (ceil(num_tokens / 128) + num_seqs) floats; may be null), that scan runs over chunks of 128 rows at once.
  * linear_attention: per head, S f32 [dk, dv] (stored [slots, H, dv, dk]): S <- a S + b k v^T, o = S^T q; q, k, v = columns off_q / off_k / off_v of
  *   proj f32 [T, ld] (head-major), through SiLU when act == 1, q also times q_scale.  gating 0: a = decay[h], b = 1.  gating 1: with i = cap
  *   tanh((proj[off_i + h] + i_bias[h]) / cap), f = logsigmoid(cap tanh((proj[off_f + h] + f_bias[h]) / cap)) and the running maximum m (0 at the
@@ -620,8 +621,8 @@ void causal_conv_ex(const float* x, int64_t ldx, const float* in_bias, const flo
 void block_diag_linear(const float* x, int64_t ldx, const float* weight, const float* bias, float* out, int64_t ldy, int32_t num_tokens, int32_t blocks,
                        int32_t rows_per_block, int32_t cols_per_block, int64_t stream);
 void gated_linear_scan(const float* u, int64_t ldu, float* gates, int64_t ld_gates, const float* lam, float* y_pre, int64_t ldy, const float* y_bias,
-                       float* state, void* out, const int32_t* cu_seqlens, const int32_t* seq_slots, const int32_t* seq_start, int32_t num_tokens, int32_t num_seqs,
-                       int32_t max_rows, int32_t channels, int32_t block_channels, float decay_scale, int32_t out_dtype, int64_t stream);
+                       float* state, void* out, float* scratch, const int32_t* cu_seqlens, const int32_t* seq_slots, const int32_t* seq_start, int32_t num_tokens,
+                       int32_t num_seqs, int32_t max_rows, int32_t channels, int32_t block_channels, float decay_scale, int32_t out_dtype, int64_t stream);
 void linear_attention(const float* proj, int64_t ld, int32_t off_q, int32_t off_k, int32_t off_v, int32_t off_i, int32_t off_f, const float* decay,
                       const float* i_bias, const float* f_bias, float gate_cap, float q_scale, int32_t act, int32_t gating, float* state, float* normaliser,
                       float* maximum, float* out, const int32_t* cu_seqlens, const int32_t* seq_slots, const int32_t* seq_start, int32_t num_tokens,

@@ -220,8 +220,22 @@ def test_recurrence_remembers_its_first_token():
     without = P.rglru_mixer(h[1:].to(F64), {k: v.to(F64) for k, v in w.items()}, 3)
     assert float((want[-1] - without[-1]).abs().max()) > 0.3 * float(want[-1].abs().max())              # the first token still counts at the end
     mix = M.GatedLinearRecurrence({k: v.to(DEV) for k, v in w.items()}, 3, 4, torch.float32)
-    state, hd = tuple(dirty(s) for s in mix.state_shapes()), dev(h)
-    close(feed(lambda b, lo, hi: mix.forward(hd[lo:hi], b, state), T, [200, 1, 1, 57]), want, 5e-5, "slow decays")
+    for sizes in ([200, 1, 1, 57], [600], [530, 3, 67]):          # from 512 rows on the scan runs over chunks of 128 rows, all at once
+        state, hd = tuple(dirty(s) for s in mix.state_shapes()), dev(h)
+        close(feed(lambda b, lo, hi: mix.forward(hd[lo:hi], b, state), T, sizes), want, 5e-5, f"slow decays, portions {sizes}")
+
+
+def test_recurrence_long_unequal_portions():
+    """two long portions of unequal length beside a short one and a single row in one step: chunk slots are counted per entry"""
+    w, g = _recurrence_case(16, 40, 5, 3, 9)
+    lens = [700, 5, 1, 513]
+    hs = [torch.randn(n, 16, generator=g) for n in lens]
+    mix = M.GatedLinearRecurrence({k: v.to(DEV) for k, v in w.items()}, 5, 3, torch.float32)
+    state = tuple(dirty(s, slots=4) for s in mix.state_shapes())
+    got = mix.forward(dev(torch.cat(hs)), step([(0, n, i) for i, n in enumerate(lens)]), state)
+    at = np.cumsum([0] + lens)
+    for i, h in enumerate(hs):
+        close(got[at[i]:at[i + 1]], P.rglru_mixer(h.to(F64), {k: v.to(F64) for k, v in w.items()}, 5), 5e-5, f"entry {i}")
 
 
 def test_recurrence_unequal_entries_and_bf16():
