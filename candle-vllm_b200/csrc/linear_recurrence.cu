@@ -932,7 +932,7 @@ la_chunk_scan_kernel(const ChunkArgs C) {
 }
 
 // o for the 64 tokens of a chunk and 64 value columns: scores against the chunk's own keys, weights, then values and entering state
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(256, 3)
 la_chunk_output_kernel(const ChunkArgs C) {
     pdl_wait();
     pdl_trigger();
@@ -969,21 +969,32 @@ la_chunk_output_kernel(const ChunkArgs C) {
     }
     const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;
     float acc[4][4] = {};
+    // a thread's eight elements of a 64 x 32 slab: (j, x) = (e >> 5, e & 31), e = thread + 256 i.  The next slab's elements are fetched into registers
+    // before the current slab is multiplied, so that the loads are in flight during the products.
+    float rq[8], rk[8];
+    auto fetch_qk = [&](int r0, bool with_k) {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            const int e = threadIdx.x + 256 * i, j = e >> 5, x = e & 31;
+            const bool ok = j < nt && r0 + x < dk;
+            const float* row = A.proj + (int64_t)(tf + (ok ? j : 0)) * A.ld;
+            rq[i] = ok ? row[A.off_q + h * dk + r0 + x] : 0.f;
+            if (with_k) rk[i] = ok ? row[A.off_k + h * dk + r0 + x] : 0.f;
+        }
+    };
     // scores: rows ty * 4 .., keys tx * 4 ..
+    fetch_qk(0, true);
     for (int r0 = 0; r0 < dk; r0 += 32) {
         __syncthreads();
-        for (int e = threadIdx.x; e < 64 * 32; e += 256) {
-            const int j = e >> 5, x = e & 31;
-            float q = 0.f, k = 0.f;
-            if (j < nt && r0 + x < dk) {
-                const float* row = A.proj + (int64_t)(tf + j) * A.ld;
-                q = row[A.off_q + h * dk + r0 + x]; k = row[A.off_k + h * dk + r0 + x];
-                if (A.act == 1) { q = silu_f(q); k = silu_f(k); }
-                q *= A.q_scale;
-            }
-            qs[x][j] = q; ks[x][j] = k;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            const int e = threadIdx.x + 256 * i, j = e >> 5, x = e & 31;
+            float q = rq[i], k = rk[i];
+            if (A.act == 1) { q = silu_f(q); k = silu_f(k); }
+            qs[x][j] = q * A.q_scale; ks[x][j] = k;
         }
         __syncthreads();
+        if (r0 + 32 < dk) fetch_qk(r0 + 32, true);
 #pragma unroll 8
         for (int x = 0; x < 32; ++x) {
             const float4 a4 = *reinterpret_cast<const float4*>(&qs[x][ty * 4]), k4 = *reinterpret_cast<const float4*>(&ks[x][tx * 4]);
@@ -993,6 +1004,13 @@ la_chunk_output_kernel(const ChunkArgs C) {
 #pragma unroll
                 for (int l = 0; l < 4; ++l) acc[i][l] = fmaf(a[i], k[l], acc[i][l]);
         }
+    }
+    // the values of the chunk travel while the weights are worked out
+    float rv[16];
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+        const int e = threadIdx.x + 256 * i, j = e >> 6, x = e & 63;
+        rv[i] = (j < nt && cv0 + x < dv) ? A.proj[(int64_t)(tf + j) * A.ld + A.off_v + h * dv + cv0 + x] : 0.f;
     }
 #pragma unroll
     for (int l = 0; l < 4; ++l) {
@@ -1005,13 +1023,23 @@ la_chunk_output_kernel(const ChunkArgs C) {
         }
         *reinterpret_cast<float4*>(&pw[j][ty * 4]) = make_float4(w[0], w[1], w[2], w[3]);
     }
-    for (int e = threadIdx.x; e < 64 * 64; e += 256) {
-        const int j = e >> 6, x = e & 63;
-        float v = 0.f;
-        if (j < nt && cv0 + x < dv) { v = A.proj[(int64_t)(tf + j) * A.ld + A.off_v + h * dv + cv0 + x]; if (A.act == 1) v = silu_f(v); }
-        vs[j][x] = v;
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+        const int e = threadIdx.x + 256 * i;
+        vs[e >> 6][e & 63] = A.act == 1 ? silu_f(rv[i]) : rv[i];
     }
     __syncthreads();
+    // the first slab of q and of the entering state for the second term travels during the first term's products
+    float ru[8];
+    auto fetch_u = [&](int r0) {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            const int e = threadIdx.x + 256 * i, j = e >> 5, x = e & 31;
+            ru[i] = (cv0 + j < dv && r0 + x < dk) ? Uin[(int64_t)(cv0 + j) * dk + r0 + x] : 0.f;
+        }
+    };
+    fetch_qk(0, false);
+    fetch_u(0);
     // first term of the output: weighted scores times values (rows ty * 4 .., columns tx * 4 ..)
     float o1[4][4] = {}, o2[4][4] = {};
     for (int j = 0; j < nt; ++j) {
@@ -1026,15 +1054,14 @@ la_chunk_output_kernel(const ChunkArgs C) {
     float (*ss)[68] = ks;                                                           // [32][68] the entering state: [key row][column], over the k slab
     for (int r0 = 0; r0 < dk; r0 += 32) {
         __syncthreads();
-        for (int e = threadIdx.x; e < 64 * 32; e += 256) {
-            const int j = e >> 5, x = e & 31;
-            float q = 0.f;
-            if (j < nt && r0 + x < dk) { q = A.proj[(int64_t)(tf + j) * A.ld + A.off_q + h * dk + r0 + x]; if (A.act == 1) q = silu_f(q); q *= A.q_scale; }
-            qs[x][j] = q;
-            // the same index pair read the other way: column j of the tile, key row x
-            ss[x][j] = (cv0 + j < dv && r0 + x < dk) ? Uin[(int64_t)(cv0 + j) * dk + r0 + x] : 0.f;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            const int e = threadIdx.x + 256 * i, j = e >> 5, x = e & 31;
+            qs[x][j] = (A.act == 1 ? silu_f(rq[i]) : rq[i]) * A.q_scale;
+            ss[x][j] = ru[i];                        // the same index pair read the other way: column j of the tile, key row x
         }
         __syncthreads();
+        if (r0 + 32 < dk) { fetch_qk(r0 + 32, false); fetch_u(r0 + 32); }
 #pragma unroll 8
         for (int x = 0; x < 32; ++x) {
             const float4 a4 = *reinterpret_cast<const float4*>(&qs[x][ty * 4]), u4 = *reinterpret_cast<const float4*>(&ss[x][tx * 4]);
