@@ -185,7 +185,8 @@ class PanaraxModel:
         pending = None                    # a sublayer's gated output that has not joined the stream yet: the next norm's kernel adds it first
         for li, L in enumerate(self.layers):
             st = state_cache[li]
-            h, h32 = ops.layer_norm(x, L.norm1, L.norm1_b, cfg.eps, dt, also_f32=L.canon is not None, pending=pending)
+            h, h32 = ops.layer_norm(x, L.norm1, L.norm1_b, cfg.eps, dt, also_f32=True, pending=pending) if L.canon is not None else \
+                (ops.layer_norm(x, L.norm1, L.norm1_b, cfg.eps, dt, pending=pending), None)
             z = ops.linear(h, L.rg1) if L.rg1 is not None else None
             if L.canon is not None:
                 hc = ops.causal_conv(h32, L.canon, st[0], batch, out_dtype=dt, add_input=True)

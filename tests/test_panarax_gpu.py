@@ -613,6 +613,16 @@ def test_unequal_batches_match_each_request_alone(name):
     assert runner.blocks.num_free_gpu_blocks() == 9 and runner.state.pool.num_free() == 3
 
 
+def test_layers_without_input_convolution_or_gates():
+    """a checkpoint that lacks the input convolutions and the residual gates of some layers: those layers run without them"""
+    cfg = CONFIGS["recurrent"]
+    w = {k: v for k, v in S.panarax_weights(cfg, 2).items() if not (k.startswith("l1.canon1") or k.startswith("l0.rg1") or k.startswith("l2.rg2"))}
+    toks = torch.randint(0, cfg["vocab"], (90,), generator=torch.Generator().manual_seed(5)).tolist()
+    ref = P.forward(cfg, w, toks)
+    model = PanaraxModel(PanaraxConfig.from_dict(cfg), w, dtype=torch.float32, block_size=64, device=DEV)
+    close(run_schedule(ModelRunner(model, 3, 1, 64), 0, toks, [40, 1, 2]), ref, TOL[torch.float32], "layers without convolution / gates")
+
+
 def test_long_decoding_and_first_tokens():
     model, toks, ref = model_and_oracle("mixed", torch.float32, 300)
     runner = ModelRunner(model, 5, 2, 64)
