@@ -27,6 +27,7 @@ from .registry import register_model, load_model  # noqa: F401
 from .gobesun import GobesunConfig, GobesunModel  # noqa: F401
 from .guvusun import GuvusunConfig, GuvusunModel  # noqa: F401
 from .panarax import PanaraxConfig, PanaraxModel  # noqa: F401
+from .dofevik import DofevikConfig, DofevikModel  # noqa: F401
 from .engine import ModelRunner, Scheduler, LLMEngine, Request  # noqa: F401
 from .moe import FusedMoe, topk_softmax, sort_expert_assignments, moe_gemm_gguf, moe_gemm_fp8  # noqa: F401
 

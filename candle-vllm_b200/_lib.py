@@ -36,26 +36,31 @@ SYMBOLS = [
     "gemm_half_q_half_alt", "b200_set_scratch",
     "linear_f32out", "rms_norm_ex", "gelu_tanh_mul", "embedding_scaled", "causal_conv_silu", "gated_delta_rule", "gated_delta_rule_tiled", "gated_delta_rule_step", "gated_rms_norm",
     "qk_norm_rope_cache", "paged_attention_varlen", "chunk_decode_view",
-    "embedding_bigram", "residual_rms_norm", "gelu_tanh_gather_mul", "latent_kv_rope_cache", "latent_q_absorb", "latent_attention_varlen", "latent_out_gate", "moe_route", "moe_gate_up", "moe_down", "mla_decode_kernel_supported", "mla_paged_attention_sink", "repack_heads", "token_tables", "linear_grouped", "moe_align_rows", "moe_align", "moe_gather_rows", "silu_mul_packed", "moe_combine_rows",
+    "embedding_bigram", "residual_rms_norm", "gelu_tanh_gather_mul", "latent_kv_rope_cache", "latent_q_absorb", "latent_attention_varlen", "latent_out_gate", "latent_out_gate_ex", "moe_route", "moe_route_bias", "moe_gate_up", "moe_gate_up_ex", "moe_down", "mla_decode_kernel_supported", "mla_paged_attention_sink", "repack_heads", "token_tables", "linear_grouped", "moe_align_rows", "moe_align", "moe_gather_rows", "silu_mul_packed", "moe_combine_rows",
     "embedding_positional", "layer_norm_ex", "gated_residual_add", "gated_add_layer_norm", "glu_packed", "group_rms_norm_gate", "head_gate", "causal_conv_ex", "block_diag_linear", "gated_linear_scan",
     "linear_attention", "linear_attention_chunked", "linear_attention_chunked_scratch", "qk_norm_rope_cache_ex", "moe_route_ex", "moe_gate_up_ex",
+    "qk_head_norm_rope_cache", "paged_attention_varlen_sink", "pooled_cache_update", "paged_attention_sigmoid_pooled", "latent_out_gate_ex", "moe_route_bias", "add_rms_norm",
 ]
 
 
 # what a library built from one source group (build.GROUPS) exports
 _COMMON = ["b200_abi_version", "b200_last_error", "b200_last_error_message", "b200_device_sm_count", "b200_device_cc", "b200_total_kernel_launches", "linear_16bit",
            "linear_f32out", "rms_norm_ex", "gelu_tanh_mul", "embedding_scaled", "argmax_f32", "rms_norm", "cast", "embedding_positional", "layer_norm_ex",
-           "gated_residual_add", "gated_add_layer_norm", "glu_packed", "group_rms_norm_gate", "head_gate"]
+           "gated_residual_add", "gated_add_layer_norm", "glu_packed", "group_rms_norm_gate", "head_gate", "add_rms_norm"]
 GROUP_SYMBOLS = {
     "ragged": _COMMON + ["causal_conv_silu", "gated_delta_rule", "gated_delta_rule_tiled", "gated_delta_rule_step", "gated_rms_norm", "qk_norm_rope_cache",
                          "paged_attention_varlen", "chunk_decode_view", "paged_attention_decode", "paged_attention_decode_workspace_bytes"],
     "latent": _COMMON + ["embedding_bigram", "residual_rms_norm", "gelu_tanh_gather_mul", "latent_kv_rope_cache", "latent_q_absorb", "latent_attention_varlen",
-                         "latent_out_gate", "moe_route", "moe_gate_up", "moe_down", "mla_decode_kernel_supported", "mla_paged_attention_sink",
+                         "latent_out_gate", "latent_out_gate_ex", "moe_route", "moe_route_bias", "moe_gate_up", "moe_gate_up_ex", "moe_down", "mla_decode_kernel_supported", "mla_paged_attention_sink",
                          "mla_paged_decode_workspace_bytes", "repack_heads", "token_tables", "linear_grouped", "moe_align_rows", "moe_align", "moe_gather_rows", "silu_mul_packed",
                          "moe_combine_rows"],
     "hybrid": _COMMON + ["causal_conv_ex", "block_diag_linear", "gated_linear_scan", "linear_attention", "linear_attention_chunked", "linear_attention_chunked_scratch", "qk_norm_rope_cache", "qk_norm_rope_cache_ex",
-                         "paged_attention_varlen", "chunk_decode_view", "paged_attention_decode", "paged_attention_decode_workspace_bytes", "moe_route", "moe_route_ex", "moe_gate_up", "moe_gate_up_ex", "moe_down", "linear_grouped",
+                         "paged_attention_varlen", "chunk_decode_view", "paged_attention_decode", "paged_attention_decode_workspace_bytes", "moe_route", "moe_route_ex", "moe_route_bias", "moe_gate_up", "moe_gate_up_ex", "moe_down", "linear_grouped",
                          "moe_align_rows", "moe_align", "moe_gather_rows", "silu_mul_packed", "moe_combine_rows"],
+    "window": _COMMON + ["qk_head_norm_rope_cache", "paged_attention_varlen_sink", "pooled_cache_update", "paged_attention_sigmoid_pooled", "latent_kv_rope_cache",
+                         "latent_q_absorb", "latent_attention_varlen", "latent_out_gate_ex", "repack_heads", "token_tables", "mla_decode_kernel_supported",
+                         "mla_paged_attention_sink", "mla_paged_decode_workspace_bytes", "moe_route_bias", "moe_gate_up_ex", "moe_down", "linear_grouped", "moe_align_rows",
+                         "moe_align", "moe_gather_rows", "moe_combine_rows"],
 }
 _RESTYPES = {"b200_last_error_message": C.c_char_p, "paged_attention_decode_workspace_bytes": C.c_size_t, "qmatmul_workspace_bytes": C.c_size_t,
              "moe_gemm_workspace_bytes": C.c_size_t, "moe_gemm_fp8_workspace_bytes": C.c_size_t, "mla_paged_decode_workspace_bytes": C.c_size_t,

@@ -43,7 +43,12 @@ GROUPS = {"ragged": ["lib", "linear_generic", "dense_gemm", "norm_act", "gated_d
           # grouped), norms, the recurrences, the SIMT attention over the paged cache and the tensor-core prefill and split-KV decode kernels it hands 128-wide
           # heads to, the expert kernels
           "hybrid": ["lib", "linear_generic", "dense_gemm", "norm_act", "linear_recurrence", "attention_varlen", "attention_prefill", "attention_decode",
-                     "attention_generic", "attention_api", "moe_ragged", "elementwise"]}
+                     "attention_generic", "attention_api", "moe_ragged", "elementwise"],
+          # softmax attention with a sink, attention without softmax over a window plus pooled blocks, latent attention, ungated routed experts: both linear
+          # kernels (the tcgen05 one also grouped), norms, the per-head preparation and pooled-cache kernels, the SIMT attention over the paged cache and the
+          # tensor-core kernels it hands 128-wide heads to, the latent mixers incl. the split-KV latent decode kernel, the expert kernels
+          "window": ["lib", "linear_generic", "dense_gemm", "norm_act", "attention_window", "attention_varlen", "attention_prefill", "attention_decode",
+                     "attention_generic", "attention_api", "latent_attention", "mla", "moe_ragged", "elementwise"]}
 
 
 def so_path(group=None) -> str:

@@ -71,15 +71,21 @@ class CacheEngine:
     def __init__(self, num_layers: int, num_kv_heads: int, head_dim: int, cache_config: CacheConfig,
                  dtype: torch.dtype = torch.bfloat16, device="cuda", num_shards: int = 1,
                  layout: int = KvLayout.FLASH, pin_cpu: bool = True,
-                 layer_shapes: Optional[Sequence[Tuple[int, int, int]]] = None):
+                 layer_shapes: Optional[Sequence[Tuple[int, int, int]]] = None, pool_shapes: Optional[Sequence[Optional[Tuple[int, int, int, int]]]] = None):
         """``layer_shapes`` (optional): one (kv heads, key size, value size) per cached layer for models whose layers differ or whose
-        keys and values have different sizes; flash layout only.  Without it every layer is (num_kv_heads, head_dim, head_dim)."""
+        keys and values have different sizes; flash layout only.  Without it every layer is (num_kv_heads, head_dim, head_dim).
+        ``pool_shapes`` (optional): per cached layer None or (entries per block, kv heads, key size, value size): the layer also keeps f32 pooled
+        keys / values [num_blocks, entries, kv heads, size] page by page (means over runs of positions that end in the page), and its cache entry
+        is the 4-tuple (K, V, pooled K, pooled V).  Pooled tensors travel with their blocks in swaps and copies."""
         self.num_layers = num_layers
         self.head_dim = head_dim
         self.num_kv_heads = max(num_kv_heads // max(num_shards, 1), 1)       # cache_engine.rs:306,320,335
         self.layer_shapes = None if layer_shapes is None else [tuple(int(v) for v in s) for s in layer_shapes]
         if self.layer_shapes is not None and (len(self.layer_shapes) != num_layers or layout != KvLayout.FLASH):
             raise BackendError("CacheEngine: layer_shapes needs one entry per layer and the flash layout")
+        self.pool_shapes = None if pool_shapes is None else [None if p is None else tuple(int(v) for v in p) for p in pool_shapes]
+        if self.pool_shapes is not None and len(self.pool_shapes) != num_layers:
+            raise BackendError("CacheEngine: pool_shapes needs one entry (or None) per layer")
         self.cfg = cache_config
         self.block_size = cache_config.block_size
         self.layout = layout
@@ -115,34 +121,43 @@ class CacheEngine:
                 kw["pin_memory"] = True
             k = torch.zeros((num_blocks,) + self.key_block_shape(i), **kw)
             v = torch.zeros((num_blocks,) + self.value_block_shape(i), **kw)
-            out.append((k, v))
+            pool = self.pool_shapes[i] if self.pool_shapes is not None else None
+            if pool is not None:
+                n, g, dk, dv = pool
+                kw["dtype"] = torch.float32
+                out.append((k, v, torch.zeros((num_blocks, n, g, dk), **kw), torch.zeros((num_blocks, n, g, dv), **kw)))
+            else:
+                out.append((k, v))
         return out
 
     def get_kv_cache(self):
         return self.gpu_cache
 
     def bytes_per_block(self) -> int:
-        return sum((k[0].numel() + v[0].numel()) * k.element_size() for k, v in self.gpu_cache)
+        return sum(t[0].numel() * t.element_size() for layer in self.gpu_cache for t in layer)
 
     def swap_in(self, src_to_dst: Dict[int, int]) -> int:
         if not self.cpu_swap_enabled:
             raise BackendError("CPU KV cache swap-in is disabled for this device")
         nbytes = 0
-        for (sk, sv), (dk, dv) in zip(self.cpu_cache, self.gpu_cache):
-            swap_blocks(sk, dk, src_to_dst)
-            swap_blocks(sv, dv, src_to_dst)
-            nbytes += (sk[0].numel() + sv[0].numel()) * sk.element_size() * len(src_to_dst)
+        for src_layer, dst_layer in zip(self.cpu_cache, self.gpu_cache):
+            for s, d in zip(src_layer, dst_layer):
+                swap_blocks(s, d, src_to_dst)
+                nbytes += s[0].numel() * s.element_size() * len(src_to_dst)
         return nbytes
 
     def swap_out(self, src_to_dst: Dict[int, int]) -> int:
         if not self.cpu_swap_enabled:
             raise BackendError("CPU KV cache swap-out is disabled for this device")
         nbytes = 0
-        for (sk, sv), (dk, dv) in zip(self.gpu_cache, self.cpu_cache):
-            swap_blocks(sk, dk, src_to_dst)
-            swap_blocks(sv, dv, src_to_dst)
-            nbytes += (sk[0].numel() + sv[0].numel()) * sk.element_size() * len(src_to_dst)
+        for src_layer, dst_layer in zip(self.gpu_cache, self.cpu_cache):
+            for s, d in zip(src_layer, dst_layer):
+                swap_blocks(s, d, src_to_dst)
+                nbytes += s[0].numel() * s.element_size() * len(src_to_dst)
         return nbytes
 
     def copy(self, src_to_dst: Dict[int, List[int]]) -> None:
-        copy_blocks([k for k, _ in self.gpu_cache], [v for _, v in self.gpu_cache], src_to_dst)
+        copy_blocks([layer[0] for layer in self.gpu_cache], [layer[1] for layer in self.gpu_cache], src_to_dst)
+        for layer in self.gpu_cache:                 # pooled entries follow their page, layer by layer (their sizes differ from layer to layer)
+            if len(layer) == 4:
+                copy_blocks([layer[2]], [layer[3]], src_to_dst)

@@ -12,7 +12,8 @@
 //                           adds a query temperature (q times 1 + coef ln(floor((p + 1) / every) + 1) at position p) and values
 //                           stored at unit root mean square per head.
 //   paged_attention_varlen  one warp per (token, head); keys in tiles of 32 (a lane scores one key, the tile's values are then
-//                           accumulated with lanes across the value columns), online softmax in f32.
+//                           accumulated with lanes across the value columns), online softmax in f32.  The _sink form puts exp(sink[h]) into
+//                           the denominator of head h (a key without a value; its score is not scaled).
 #include <stdlib.h>
 
 #include "attention.cuh"
@@ -110,7 +111,7 @@ __global__ void __launch_bounds__(128)
 paged_attention_varlen_kernel(const TQ* __restrict__ q, const TC* __restrict__ k_cache, const TC* __restrict__ v_cache,
                               const int32_t* __restrict__ block_tables, int table_width, const int32_t* __restrict__ token_seq,
                               const int32_t* __restrict__ positions, TOut* __restrict__ out, int64_t items, int H, int G, int dk, int dv,
-                              int block_size, float scale, int chunk, int window) {
+                              int block_size, float scale, int chunk, int window, const float* __restrict__ sink) {
     pdl_wait();
     pdl_trigger();
     extern __shared__ float qsm[];                  // [4 warps][dk]
@@ -128,7 +129,8 @@ paged_attention_varlen_kernel(const TQ* __restrict__ q, const TC* __restrict__ k
     int lo = 0;
     if (chunk > 0) lo = (pos / chunk) * chunk;
     if (window > 0 && pos - window + 1 > lo) lo = pos - window + 1;
-    float m = -INFINITY, l = 0.f;
+    // a sink is a key without a value whose score is sink[h] as it stands: the running maximum and sum start from it
+    float m = sink ? sink[h] : -INFINITY, l = sink ? 1.f : 0.f;
     float acc[kMaxVPerLane];
 #pragma unroll
     for (int c = 0; c < kMaxVPerLane; ++c) acc[c] = 0.f;
@@ -225,6 +227,15 @@ void paged_attention_varlen(void* out, const void* q, const void* key_cache, con
                             const int32_t* cu_seqlens_k, int32_t num_seqs, int32_t num_tokens, int32_t num_heads, int32_t num_kv_heads, int32_t dk,
                             int32_t dv, int32_t block_size, float scale, int32_t chunk, int32_t window, int32_t q_dtype, int32_t cache_dtype,
                             int32_t out_dtype, int64_t stream) {
+    paged_attention_varlen_sink(out, q, key_cache, value_cache, block_tables, table_width, token_seq, positions, cu_seqlens_q, cu_seqlens_k, num_seqs, num_tokens,
+                                num_heads, num_kv_heads, dk, dv, block_size, scale, chunk, window, nullptr, q_dtype, cache_dtype, out_dtype, stream);
+}
+
+void paged_attention_varlen_sink(void* out, const void* q, const void* key_cache, const void* value_cache, const int32_t* block_tables,
+                                 int32_t table_width, const int32_t* token_seq, const int32_t* positions, const int32_t* cu_seqlens_q,
+                                 const int32_t* cu_seqlens_k, int32_t num_seqs, int32_t num_tokens, int32_t num_heads, int32_t num_kv_heads, int32_t dk,
+                                 int32_t dv, int32_t block_size, float scale, int32_t chunk, int32_t window, const float* sink, int32_t q_dtype,
+                                 int32_t cache_dtype, int32_t out_dtype, int64_t stream) {
     if (num_tokens == 0) return;
     B200_REQUIRE(out && q && key_cache && value_cache && block_tables && token_seq && positions, kErrBadArg, "paged_attention_varlen: null pointer");
     B200_REQUIRE(num_heads > 0 && num_kv_heads > 0 && num_heads % num_kv_heads == 0 && dk > 0 && dv > 0 && block_size > 0 && table_width > 0,
@@ -233,7 +244,7 @@ void paged_attention_varlen(void* out, const void* q, const void* key_cache, con
     // 16-bit q / cache / out with 128-wide heads and 64-token blocks: the tensor-core kernel that serves the other models' prefill
     // (attention_prefill.cu), with the chunk rule added to its mask; it covers portions and single tokens alike
     static const bool no_tc = [] { const char* e = getenv("B200_VARLEN_SIMT"); return e && atoi(e) != 0; }();
-    if (!no_tc && q_dtype == B200_BF16 && out_dtype == B200_BF16 && dk == dv && cu_seqlens_q && cu_seqlens_k && num_seqs > 0 &&
+    if (!no_tc && !sink && q_dtype == B200_BF16 && out_dtype == B200_BF16 && dk == dv && cu_seqlens_q && cu_seqlens_k && num_seqs > 0 &&
         paged_attention_prefill_tc_supported(dk, block_size, B200_BF16, cache_dtype, B200_KV_FLASH, 0.f, 1, q, key_cache, value_cache)) {
         paged_attention_prefill_tc(out, q, key_cache, value_cache, (const uint32_t*)block_tables, (const uint32_t*)cu_seqlens_q,
                                    (const uint32_t*)cu_seqlens_k, num_seqs, num_tokens, num_heads, num_kv_heads, table_width, (int64_t)1 << 22, scale,
@@ -246,7 +257,7 @@ void paged_attention_varlen(void* out, const void* q, const void* key_cache, con
     const unsigned grid = (unsigned)((items + 3) / 4);
     const size_t smem = (size_t)4 * dk * sizeof(float);
 #define PAV(TC, TO, TQ) launch_pdl(paged_attention_varlen_kernel<TC, TO, TQ>, dim3(grid), dim3(128), smem, st, (const TQ*)q, (const TC*)key_cache, \
-        (const TC*)value_cache, block_tables, table_width, token_seq, positions, (TO*)out, items, num_heads, num_kv_heads, dk, dv, block_size, scale, chunk, window)
+        (const TC*)value_cache, block_tables, table_width, token_seq, positions, (TO*)out, items, num_heads, num_kv_heads, dk, dv, block_size, scale, chunk, window, sink)
     if (cache_dtype == B200_F32 && out_dtype == B200_F32 && q_dtype == B200_F32) PAV(float, float, float);
     else if (cache_dtype == B200_BF16 && out_dtype == B200_BF16 && q_dtype == B200_F32) PAV(__nv_bfloat16, __nv_bfloat16, float);
     else if (cache_dtype == B200_BF16 && out_dtype == B200_BF16 && q_dtype == B200_BF16) PAV(__nv_bfloat16, __nv_bfloat16, __nv_bfloat16);

@@ -17,7 +17,8 @@
 //                            the group, a lane scores one key, then the tile's latents are accumulated with lanes across the
 //                            latent columns; online softmax in f32 that starts from the sink.  Steps of few rows cut every row's keys into
 //                            `splits` runs (one block each) whose (max, sum, weighted sum) a second kernel folds.
-//   latent_out_gate          out as above (w_uv = null: the product was done by the GEMM, only the gate and the cast remain).
+//   latent_out_gate          out as above (w_uv = null: the product was done by the GEMM, only the gate and the cast remain).  The _ex form may take
+//                            one gate per output entry (gate [T, H dv]) instead of one per head.
 #include "common.cuh"
 
 namespace b200 {
@@ -225,17 +226,19 @@ latent_attention_merge_kernel(const float* __restrict__ part, TO* __restrict__ o
 template <typename TW, typename TOut>
 __global__ void __launch_bounds__(128)
 latent_out_gate_kernel(const float* __restrict__ src, int64_t s_st, int64_t s_sh, const TW* __restrict__ w_uv, const float* __restrict__ gate,
-                       int64_t ld_gate, TOut* __restrict__ out, int H, int dv, int R) {
+                       int64_t ld_gate, TOut* __restrict__ out, int H, int dv, int R, int gate_per_element) {
     pdl_wait();
     pdl_trigger();
     extern __shared__ float ol[];                          // [R]
     const int t = blockIdx.x, h = blockIdx.y;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const float gv = gate ? 1.0f / (1.0f + expf(-gate[(int64_t)t * ld_gate + h])) : 1.0f;
+    // one gate per head, or (gate_per_element) one per output entry: gate [T, H dv]
+    const float* ge = gate && gate_per_element ? gate + (int64_t)t * ld_gate + (int64_t)h * dv : nullptr;
+    const float gv = gate && !ge ? 1.0f / (1.0f + expf(-gate[(int64_t)t * ld_gate + h])) : 1.0f;
     TOut* o = out + ((int64_t)t * H + h) * dv;
     const float* sp = src + (int64_t)t * s_st + (int64_t)h * s_sh;
     if (!w_uv) {                                           // src holds the dv values already
-        for (int i = threadIdx.x; i < dv; i += 128) o[i] = from_f32<TOut>(sp[i] * gv);
+        for (int i = threadIdx.x; i < dv; i += 128) o[i] = from_f32<TOut>(sp[i] * (ge ? 1.0f / (1.0f + expf(-ge[i])) : gv));
         return;
     }
     for (int i = threadIdx.x; i < R; i += 128) ol[i] = sp[i];
@@ -245,7 +248,7 @@ latent_out_gate_kernel(const float* __restrict__ src, int64_t s_st, int64_t s_sh
         float a = 0.f;
         for (int r = lane; r < R; r += 32) a = fmaf(ol[r], to_f32<TW>(w[(int64_t)d * R + r]), a);
         a = warp_sum(a);
-        if (lane == 0) o[d] = from_f32<TOut>(a * gv);
+        if (lane == 0) o[d] = from_f32<TOut>(a * (ge ? 1.0f / (1.0f + expf(-ge[d])) : gv));
     }
 }
 
@@ -376,14 +379,20 @@ void latent_attention_varlen(void* o_lat, int64_t o_stride_token, int64_t o_stri
 
 void latent_out_gate(const float* src, int64_t src_stride_token, int64_t src_stride_head, const void* w_uv, const float* gate, int64_t ld_gate, void* out,
                      int32_t num_tokens, int32_t num_heads, int32_t dv, int32_t rank, int32_t w_dtype, int32_t out_dtype, int64_t stream) {
+    latent_out_gate_ex(src, src_stride_token, src_stride_head, w_uv, gate, ld_gate, 0, out, num_tokens, num_heads, dv, rank, w_dtype, out_dtype, stream);
+}
+
+void latent_out_gate_ex(const float* src, int64_t src_stride_token, int64_t src_stride_head, const void* w_uv, const float* gate, int64_t ld_gate,
+                        int32_t gate_per_element, void* out, int32_t num_tokens, int32_t num_heads, int32_t dv, int32_t rank, int32_t w_dtype, int32_t out_dtype,
+                        int64_t stream) {
     if (num_tokens == 0) return;
-    B200_REQUIRE(src && out && num_heads > 0 && num_heads <= 65535 && dv > 0 && rank > 0 && rank <= 8192 && (!gate || ld_gate >= num_heads), kErrBadArg,
-                 "latent_out_gate: bad arguments");
+    B200_REQUIRE(src && out && num_heads > 0 && num_heads <= 65535 && dv > 0 && rank > 0 && rank <= 8192 &&
+                 (!gate || ld_gate >= (int64_t)num_heads * (gate_per_element ? dv : 1)), kErrBadArg, "latent_out_gate: bad arguments");
     cudaStream_t st = as_stream(stream);
     const size_t smem = (size_t)rank * sizeof(float);
     const dim3 grid(num_tokens, num_heads);
 #define LOG(TW, TO) launch_pdl(latent_out_gate_kernel<TW, TO>, grid, dim3(128), smem, st, src, src_stride_token, src_stride_head, (const TW*)w_uv, gate, ld_gate, (TO*)out, \
-                               num_heads, dv, rank)
+                               num_heads, dv, rank, gate_per_element)
     if (w_dtype == B200_F32 && out_dtype == B200_F32) LOG(float, float);
     else if (w_dtype == B200_BF16 && out_dtype == B200_BF16) LOG(__nv_bfloat16, __nv_bfloat16);
     else if (w_dtype == B200_BF16 && out_dtype == B200_F32) LOG(__nv_bfloat16, float);

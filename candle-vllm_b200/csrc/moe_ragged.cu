@@ -6,9 +6,11 @@
 //                     outputs form `groups` equal runs of neighbours, a group's score is its best choice score, and only members of the
 //                     `keep` best groups can be chosen (the others count as -inf); the `top` best choice scores are taken (ties: the lower
 //                     index); weights = s of the chosen / (their sum + 1e-20) * scale.  groups <= 1 switches the restriction off.
-//                     The _ex form takes the scores from a sigmoid per output instead of the softmax, and may leave the chosen scores as they are.
+//                     The _ex form takes the scores from a sigmoid per output instead of the softmax, and may leave the chosen scores as they are; the
+//                     _bias form first adds a bias to the logits (softmax over all outputs, renormalised over the chosen = softmax over the chosen logits).
 //   moe_gate_up       act[p] = silu(W_gate[e] h) * (W_up[e] h); the _ex form may first multiply both products by the pair's weight (an expert fed its
-//                     token times the router's score) and has the clamped activation of glu_packed.  Pair p = (token, choice) with expert e < E; outputs
+//                     token times the router's score) and has the clamped activation of glu_packed, and the ungated form act[p] = relu(W_up[e] h)^2 with
+//                     one matrix [ff, D] per expert.  Pair p = (token, choice) with expert e < E; outputs
 //                     e >= E are identity experts (no weights) and are skipped.
 //   moe_down          y[row] = W_down[e] act[p] for the pairs in expert order (moe_align with tiles of one row);
 //   moe_combine_rows  out[t] = sum over the token's choices, in choice order, of weight * y[row of the pair], or weight * x[t] for an
@@ -23,7 +25,7 @@ namespace {
 
 __global__ void __launch_bounds__(32)
 moe_route_kernel(const float* __restrict__ logits, int64_t ld, const float* __restrict__ correction, int32_t* __restrict__ ids, float* __restrict__ weights,
-                 int N, int top, int groups, int keep, float scale, int score_fn, int normalise) {
+                 int N, int top, int groups, int keep, float scale, int score_fn, int normalise, const float* __restrict__ logit_bias) {
     pdl_wait();
     pdl_trigger();
     extern __shared__ float sm[];
@@ -32,6 +34,12 @@ moe_route_kernel(const float* __restrict__ logits, int64_t ld, const float* __re
     float* gbest = sm + 2 * N;     // [groups]
     const int t = blockIdx.x, lane = threadIdx.x;
     const float* z = logits + (int64_t)t * ld;
+    if (logit_bias) {                                      // a bias that belongs to the logits: it counts for the choice and for the weights
+        float* zb = sm + 2 * N + (groups > 1 ? groups : 1);
+        for (int i = lane; i < N; i += 32) zb[i] = z[i] + logit_bias[i];
+        __syncwarp();
+        z = zb;
+    }
     if (score_fn == 1) {
         for (int i = lane; i < N; i += 32) { s[i] = 1.0f / (1.0f + expf(-z[i])); pick[i] = s[i] + (correction ? correction[i] : 0.f); }
     } else {
@@ -134,15 +142,20 @@ moe_gate_up_kernel(const T* __restrict__ h, int64_t ldh, const T* __restrict__ w
     const bool vec = rows_vectorise<T>(w_gu, D, D);
     for (int i = threadIdx.x; i < D; i += 128) hs[staged_at<T>(i, D, vec)] = to_f32<T>(h[t * ldh + i]);
     __syncthreads();
-    const T* wg = w_gu + (int64_t)e * 2 * ff * D;           // [gate rows | up rows][D]
+    const bool gated = act_fn != 3;                         // ungated experts keep one matrix [ff, D] in front of the activation
+    const T* wg = w_gu + (int64_t)e * (gated ? 2 : 1) * ff * D;           // [gate rows | up rows][D]
     const int j1 = min(ff, (int)(blockIdx.y + 1) * kGuRows);
     for (int j = blockIdx.y * kGuRows + warp; j < j1; j += 4) {
-        float a = row_dot<T>(wg + (int64_t)j * D, hs, D, lane, vec), b = row_dot<T>(wg + (int64_t)(ff + j) * D, hs, D, lane, vec);
-        a = warp_sum(a); b = warp_sum(b);
+        float a = row_dot<T>(wg + (int64_t)j * D, hs, D, lane, vec), b = gated ? row_dot<T>(wg + (int64_t)(ff + j) * D, hs, D, lane, vec) : 0.f;
+        a = warp_sum(a);
+        if (gated) b = warp_sum(b);
         if (lane == 0) {
             if (pair_scale) { const float sc = pair_scale[p]; a *= sc; b *= sc; }         // the expert sees its token times the pair's weight
             float v;
-            if (act_fn == 2) {
+            if (act_fn == 3) {
+                a = fmaxf(a, 0.f);
+                v = a * a;
+            } else if (act_fn == 2) {
                 a = fminf(a, limit); b = fminf(fmaxf(b, -limit), limit);
                 v = a / (1.0f + expf(-1.702f * a)) * (b + 1.0f);
             } else {
@@ -265,14 +278,20 @@ void moe_route(const float* logits, int64_t ld, const float* correction, int32_t
 
 void moe_route_ex(const float* logits, int64_t ld, const float* correction, int32_t* ids, float* weights, int32_t num_tokens, int32_t num_outputs, int32_t top,
                   int32_t groups, int32_t keep, float scale, int32_t score_fn, int32_t normalise, int64_t stream) {
+    moe_route_bias(logits, ld, nullptr, correction, ids, weights, num_tokens, num_outputs, top, groups, keep, scale, score_fn, normalise, stream);
+}
+
+void moe_route_bias(const float* logits, int64_t ld, const float* logit_bias, const float* correction, int32_t* ids, float* weights, int32_t num_tokens,
+                    int32_t num_outputs, int32_t top, int32_t groups, int32_t keep, float scale, int32_t score_fn, int32_t normalise, int64_t stream) {
     if (num_tokens == 0) return;
     B200_REQUIRE(logits && ids && weights && num_outputs > 0 && top > 0 && top <= num_outputs && ld >= num_outputs, kErrBadArg, "moe_route: bad arguments");
     B200_REQUIRE(groups <= 1 || (num_outputs % groups == 0 && keep > 0 && keep <= groups), kErrBadArg, "moe_route: %d outputs do not form %d equal groups (keep %d)",
                  num_outputs, groups, keep);
     B200_REQUIRE(num_outputs <= 8192, kErrUnsupported, "moe_route: more than 8192 router outputs");
-    const size_t smem = ((size_t)2 * num_outputs + (groups > 1 ? groups : 1)) * sizeof(float);
+    const size_t smem = ((size_t)(logit_bias ? 3 : 2) * num_outputs + (groups > 1 ? groups : 1)) * sizeof(float);
+    ensure_dynamic_smem(reinterpret_cast<const void*>(moe_route_kernel), (int)smem);
     launch_pdl(moe_route_kernel, dim3(num_tokens), dim3(32), smem, as_stream(stream), logits, ld, correction, ids, weights, num_outputs, top, groups, keep, scale,
-               score_fn, normalise);
+               score_fn, normalise, logit_bias);
     count_launch();
     check_launch("moe_route");
 }
@@ -285,7 +304,7 @@ void moe_gate_up(const void* h, int64_t ldh, const void* w_gate_up, const int32_
 void moe_gate_up_ex(const void* h, int64_t ldh, const void* w_gate_up, const int32_t* ids, const int32_t* order, void* act, int32_t num_tokens, int32_t top,
                     int32_t num_experts, int32_t ff, int32_t width, int32_t act_fn, float limit, const float* pair_scale, int32_t dtype, int64_t stream) {
     if (num_tokens == 0 || num_experts == 0) return;
-    B200_REQUIRE(act_fn == 0 || act_fn == 2, kErrBadArg, "moe_gate_up: activation %d (0 = SiLU, 2 = clamped)", act_fn);
+    B200_REQUIRE(act_fn == 0 || act_fn == 2 || act_fn == 3, kErrBadArg, "moe_gate_up: activation %d (0 = SiLU, 2 = clamped, 3 = ungated squared ReLU)", act_fn);
     B200_REQUIRE(h && w_gate_up && ids && act && top > 0 && ff > 0 && width > 0 && width <= 16384 && ldh >= width, kErrBadArg, "moe_gate_up: bad arguments");
     cudaStream_t st = as_stream(stream);
     const dim3 grid((unsigned)((int64_t)num_tokens * top), (unsigned)((ff + kGuRows - 1) / kGuRows));

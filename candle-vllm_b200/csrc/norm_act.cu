@@ -17,7 +17,10 @@
 //   gated_add_layer_norm  both of the above in one pass over the row: the closing sum of a sublayer, then the next sublayer's norm of the new x;
 //   glu_packed       out = act(gate) * up from a packed [rows, 2 ff] product, act one of silu, tanh GELU, or the clamped form
 //                    g' = min(g, limit), u' = clamp(u, +-limit), g' sigmoid(1.702 g') (u' + 1); a per-row factor may multiply gate and
-//                    up first (an expert that sees its token times the router's score);
+//                    up first (an expert that sees its token times the router's score); act 3 is ungated: out = relu(g)^2 from rows of ff entries;
+//   add_rms_norm     the pre-norm step on the f32 stream: x <- x + y1 + y2 (each optional; x in place), then out = x / sqrt(mean(x^2) + eps) * w
+//                    in the compute dtype for the next product -- the closing sum of one sublayer and the opening norm of the next in one pass;
+//                    with `row_index` only the selected rows are summed and normed and x is left as it is; w null = the sum alone;
 //   group_rms_norm_gate  out = o / rms(o over a group of neighbours) * w * act(gate): the closing norm of the linear-attention mixers,
 //                    one group per head or one for the whole row;
 //   head_gate        out[t, h, :] = src[t, h, :] * sigmoid(gate[t, h]): one gate per attention head.
@@ -231,13 +234,14 @@ __global__ void glu_packed_kernel(const float* __restrict__ gu, TOut* __restrict
     if (i >= rows * ff) return;
     const int64_t r = i / ff;
     const int c = (int)(i - r * ff);
-    float g = gu[r * ld + c], u = gu[r * ld + ff + c];
+    float g = gu[r * ld + c], u = act == 3 ? 0.f : gu[r * ld + ff + c];        // act 3 is ungated: the row holds ff entries only
     if (row_scale) {
         const int64_t j = scale_index ? scale_index[r] : r;
         if (j < 0) { out[i] = from_f32<TOut>(0.f); return; }          // a padding row of a sorted, tiled order
         const float s = row_scale[j];
         g *= s; u *= s;
     }
+    if (act == 3) { g = fmaxf(g, 0.f); out[i] = from_f32<TOut>(g * g); return; }
     out[i] = from_f32<TOut>(glu_value(g, u, act, limit));
 }
 
@@ -321,6 +325,38 @@ gated_add_layer_norm_kernel(float* __restrict__ x, const float* __restrict__ y, 
         const float v = fmaf((xr[i] - mean) * sc, w[i], b ? b[i] : 0.f);
         if (out) out[row * n + i] = from_f32<TOut>(v);
         if (out32) out32[row * n + i] = v;
+    }
+}
+
+
+template <typename TOut>
+__global__ void __launch_bounds__(256)
+add_rms_norm_kernel(float* __restrict__ x, const float* __restrict__ y1, int64_t ld1, const float* __restrict__ y2, int64_t ld2, const float* __restrict__ w,
+                    TOut* __restrict__ out, const int32_t* __restrict__ row_index, int n, float eps) {
+    pdl_wait();
+    pdl_trigger();
+    __shared__ float red[8];
+    const int row = blockIdx.x;
+    const int64_t src = row_index ? row_index[row] : row;
+    float* xr = x + src * n;
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < n; i += 256) {
+        float v = xr[i];
+        if (y1) v += y1[src * ld1 + i];
+        if (y2) v += y2[src * ld2 + i];
+        if (!row_index && (y1 || y2)) xr[i] = v;
+        ss = fmaf(v, v, ss);
+    }
+    if (!out) return;
+    const float tot = block_sum_256(ss, red);
+    const float sc = 1.0f / sqrtf(tot / (float)n + eps);
+    for (int i = threadIdx.x; i < n; i += 256) {
+        float v = xr[i];
+        if (row_index) {                                   // x was not updated: form the sum again
+            if (y1) v += y1[src * ld1 + i];
+            if (y2) v += y2[src * ld2 + i];
+        }
+        out[(int64_t)row * n + i] = from_f32<TOut>(v * sc * w[i]);
     }
 }
 
@@ -458,7 +494,7 @@ void gated_residual_add(float* x, const float* y, int64_t ldy, const float* gate
 void glu_packed(const float* gate_up, void* out, int64_t rows, int32_t ff, int64_t ld, int32_t act, float limit, const float* row_scale, const int32_t* scale_index,
                 int32_t out_dtype, int64_t stream) {
     if (rows == 0 || ff == 0) return;
-    B200_REQUIRE(gate_up && out && rows > 0 && ff > 0 && ld >= 2 * (int64_t)ff && act >= 0 && act <= 2 && (row_scale || !scale_index), kErrBadArg,
+    B200_REQUIRE(gate_up && out && rows > 0 && ff > 0 && ld >= (act == 3 ? 1 : 2) * (int64_t)ff && act >= 0 && act <= 3 && (row_scale || !scale_index), kErrBadArg,
                  "glu_packed: bad arguments");
     const unsigned grid = (unsigned)((rows * ff + 255) / 256);
     cudaStream_t st = as_stream(stream);
@@ -516,6 +552,18 @@ void gated_add_layer_norm(float* x, const float* y, int64_t ldy, const float* ga
     else { set_error(kErrUnsupported, "gated_add_layer_norm: out dtype %d (f32 / bf16)", out_dtype); return; }
     count_launch();
     check_launch("gated_add_layer_norm");
+}
+
+void add_rms_norm(float* x, const float* y1, int64_t ld1, const float* y2, int64_t ld2, const float* weight, void* out, const int32_t* row_index, int32_t rows,
+                  int32_t n, float eps, int32_t out_dtype, int64_t stream) {
+    if (rows == 0) return;
+    B200_REQUIRE(x && rows > 0 && n > 0 && (!y1 || ld1 >= n) && (!y2 || ld2 >= n) && ((weight == nullptr) == (out == nullptr)), kErrBadArg, "add_rms_norm: bad arguments");
+    cudaStream_t st = as_stream(stream);
+    if (!out || out_dtype == B200_F32) launch_pdl(add_rms_norm_kernel<float>, dim3(rows), dim3(256), 0, st, x, y1, ld1, y2, ld2, weight, (float*)out, row_index, n, eps);
+    else if (out_dtype == B200_BF16) launch_pdl(add_rms_norm_kernel<__nv_bfloat16>, dim3(rows), dim3(256), 0, st, x, y1, ld1, y2, ld2, weight, (__nv_bfloat16*)out, row_index, n, eps);
+    else { set_error(kErrUnsupported, "add_rms_norm: out dtype %d (f32 / bf16)", out_dtype); return; }
+    count_launch();
+    check_launch("add_rms_norm");
 }
 
 }  // extern "C"

@@ -81,7 +81,8 @@ class ModelRunner:
         self.model, self.block_size = model, block_size
         plan = model.cache_plan()
         kv = plan["kv_layers"]
-        self.cache = CacheEngine(len(kv), 0, 0, CacheConfig(block_size, num_blocks), dtype=model.dtype, device=model.device, layer_shapes=kv) if kv else None
+        self.cache = CacheEngine(len(kv), 0, 0, CacheConfig(block_size, num_blocks), dtype=model.dtype, device=model.device, layer_shapes=kv,
+                                 pool_shapes=plan.get("pool_layers")) if kv else None
         self.state = StateCache(plan["state_layers"], num_slots, device=model.device)
         self.blocks = BlockManager(block_size, num_blocks, 0)
         self.lengths: Dict[int, int] = {}          # tokens of each live sequence already in cache / state

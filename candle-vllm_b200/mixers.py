@@ -37,12 +37,15 @@ def yarn_rotary_tables(dims: int, base: float, max_pos: int, scaling: Optional[d
     """cos / sin f32 [max_pos, dims/2] for the rotate-half layout, angles computed in float64.  ``scaling`` = dict(factor, original, fast,
     slow) applies YaRN: with c(t) = dims * ln(original / (2 pi t)) / (2 ln base), lo = max(floor(c(fast)), 0), hi = min(ceil(c(slow)),
     dims - 1) and r_i = clamp((i - lo) / max(hi - lo, 0.001), 0, 1), frequency i becomes f_i / factor * r_i + f_i * (1 - r_i), and cos /
-    sin are multiplied by 0.1 * ln(factor) + 1."""
+    sin are multiplied by 0.1 * ln(factor) + 1.  A ``scaling`` of dict(factor) alone is linear scaling: every frequency is divided by the factor.
+    Row p holds the angles p f_i whatever the pairing of the entries (neighbours or half apart) the kernel that reads the table uses."""
     half = dims // 2
     i = torch.arange(half, dtype=torch.float64)
     f = float(base) ** (-2.0 * i / dims)
     mag = 1.0
-    if scaling:
+    if scaling and "original" not in scaling:
+        f = f / float(scaling.get("factor", 1.0))
+    elif scaling:
         factor, original = float(scaling["factor"]), float(scaling["original"])
         corr = lambda turns: dims * math.log(original / (2.0 * math.pi * turns)) / (2.0 * math.log(base))
         lo = max(math.floor(corr(float(scaling["fast"]))), 0)
@@ -90,16 +93,32 @@ class PagedAttentionMixer:
     """weights: q [H dk, D], k [G dk, D], v [G dv, D], o [D, H dv]; optional q.norm [H dk], k.norm [G dk] (plain weights, RMS over the whole
     row), optional g [H, D] (head h's output times sigmoid(g x)[h]).  rot = dict(dims, base, scaling) or None; chunk / window = 0 for none;
     q_temp = dict(coef, every): the query at position p times 1 + coef ln(floor((p + 1) / every) + 1); value_norm: every value head is
-    cached divided by its root mean square."""
+    cached divided by its root mean square.
+
+    ``head_norm`` "before" / "after": q and k are normed head by head over dk, before or after the rotation (q.norm / k.norm are then [dk], shared by the
+    heads, or absent for a norm without weight); ``interleaved``: the rotation pairs neighbours (2i, 2i + 1) instead of (i, i + dims/2); biases q.b / k.b /
+    v.b are added in the projection; sink [H]: exp(sink[h]) joins the softmax denominator of head h (a key without a value whose score is not scaled)."""
     kind = "kv"
 
     def __init__(self, w: Dict[str, torch.Tensor], heads: int, kv_heads: int, dk: int, dv: int, scale: float, eps: float, dtype: torch.dtype,
                  rot: Optional[dict] = None, chunk: int = 0, window: int = 0, block_size: int = 64, max_pos: int = 4096, q_temp: Optional[dict] = None,
-                 value_norm: bool = False):
+                 value_norm: bool = False, head_norm: str = "none", interleaved: bool = False):
         if heads % kv_heads:
             raise BackendError("PagedAttentionMixer: heads must be a multiple of kv_heads")
+        if head_norm not in ("none", "before", "after") or (head_norm != "none" and (q_temp or value_norm)):
+            raise BackendError(f"PagedAttentionMixer: head_norm {head_norm!r} (none / before / after; not with a query temperature or normed values)")
         self.H, self.G, self.dk, self.dv, self.scale, self.eps, self.dtype = heads, kv_heads, dk, dv, float(scale), eps, dtype
         self.chunk, self.window, self.block_size, self.rot = int(chunk), int(window), block_size, rot
+        self.head_norm, self.interleaved = head_norm, bool(interleaved)
+        self.sink = w["sink"].float().contiguous() if "sink" in w else None
+        self.bias = None
+        if any(n + ".b" in w for n in "qkv"):
+            zero = lambda n: torch.zeros(w[n].shape[0], dtype=torch.float32, device=w[n].device)
+            self.bias = torch.cat([w[n + ".b"].float() if n + ".b" in w else zero(n) for n in "qkv"], 0).contiguous()
+        # the per-head preparation kernel serves head norms, neighbour pairs and biases; the whole-row one the rest
+        self.per_head = head_norm != "none" or self.interleaved or self.bias is not None
+        if self.per_head and (q_temp or value_norm):
+            raise BackendError("PagedAttentionMixer: biases / neighbour pairs do not combine with a query temperature or normed values")
         self.has_gate = "g" in w
         self.off_g = heads * dk + kv_heads * (dk + dv)
         self.w_in = torch.cat([w["q"], w["k"], w["v"]] + ([w["g"]] if self.has_gate else []), 0).to(dtype).contiguous()
@@ -114,12 +133,15 @@ class PagedAttentionMixer:
         # 16-bit q for the tensor-core attention kernel (128-wide heads, 64-token blocks, bf16 cache); f32 q for the SIMT one
         self.q_dtype = torch.bfloat16 if (dtype == torch.bfloat16 and dk == dv == 128 and block_size == 64) else torch.float32
         # steps of single tokens: the split-KV decode kernel, when chunks start on block borders and the head layout is one it takes
-        self.decode_kernel = (self.q_dtype == torch.bfloat16 and self.chunk % block_size == 0 and self.window == 0 and heads // kv_heads in (1, 2, 4, 8))
+        self.decode_kernel = (self.q_dtype == torch.bfloat16 and self.chunk % block_size == 0 and self.window == 0 and heads // kv_heads in (1, 2, 4, 8) and
+                              self.sink is None)
         self._scratch = {}
         self.cos = self.sin = None
         self._device = self.w_in.device
         if rot:
             self.ensure_positions(max_pos)
+        if self.q_norm is not None and self.q_norm.numel() != (dk if head_norm != "none" else heads * dk):
+            raise BackendError(f"PagedAttentionMixer: q.norm has {self.q_norm.numel()} entries for head_norm {head_norm!r}")
 
     def ensure_positions(self, max_pos: int) -> None:
         if self.rot and (self.cos is None or self.cos.shape[0] < max_pos):
@@ -135,8 +157,12 @@ class PagedAttentionMixer:
             self.ensure_positions(max(2 * self.cos.shape[0], batch.max_position + 1))
         if proj is None:
             proj = ops.linear(h, self.w_in)
-        q = ops.qk_norm_rope_cache(proj, self.q_norm, self.k_norm, self.cos, self.sin, batch, k_cache, v_cache, self.H, self.G, self.dk, self.dv,
-                                   self.rot_dims, self.eps, self.q_dtype, q_temp=self.q_temp, v_unit_rms=self.value_norm)
+        if self.per_head:
+            q = ops.qk_head_norm_rope_cache(proj, self.bias, self.q_norm, self.k_norm, self.cos, self.sin, batch, k_cache, v_cache, self.H, self.G, self.dk, self.dv,
+                                            self.rot_dims, self.eps, interleaved=self.interleaved, norm=self.head_norm, q_dtype=self.q_dtype)
+        else:
+            q = ops.qk_norm_rope_cache(proj, self.q_norm, self.k_norm, self.cos, self.sin, batch, k_cache, v_cache, self.H, self.G, self.dk, self.dv,
+                                       self.rot_dims, self.eps, self.q_dtype, q_temp=self.q_temp, v_unit_rms=self.value_norm)
         if self.decode_kernel and batch.pure_decode and batch.num_seqs <= 256:
             # without a chunk mask the whole table is one chunk
             a = ops.paged_attention_decode_chunked(q, k_cache, v_cache, batch, self.H, self.G, self.dk, self.block_size, self.scale,
@@ -144,10 +170,56 @@ class PagedAttentionMixer:
         else:
             # on the SIMT kernel gated head outputs stay f32 until the gate has been applied and take the compute dtype once; the tensor-core kernel
             # (16-bit q) returns 16 bits
-            a = ops.paged_attention_varlen(q, k_cache, v_cache, batch, self.H, self.G, self.dk, self.dv, self.block_size, self.scale, self.chunk,
-                                           self.window, torch.float32 if (self.has_gate and self.q_dtype == torch.float32) else self.dtype)
+            a = ops.paged_attention_varlen_sink(q, k_cache, v_cache, batch, self.H, self.G, self.dk, self.dv, self.block_size, self.scale, self.chunk,
+                                                self.window, self.sink, torch.float32 if (self.has_gate and self.q_dtype == torch.float32) else self.dtype)
         if self.has_gate:
             a = ops.head_gate(a, proj[:, self.off_g:], self.H, self.dv, self.dtype)
+        return ops.linear(a, self.w_o)
+
+
+class PooledWindowAttentionMixer:
+    """Grouped-query attention without a softmax: the weight of a visible key is sigmoid(q . k scale + pb[h]), and the weights are not normalised over the
+    keys.  A query at position i sees the tokens j with 0 <= i - j < window and, beside them and treated like them, one mean key / mean value per block of
+    ``pool`` positions that lies wholly before the window (block b = positions b pool .. b pool + pool - 1, seen once b pool + pool - 1 <= i - window).
+    q and k are normed head by head (weights q.norm / k.norm [dk] shared by the heads), nothing is rotated, and the value of a token is its key as projected
+    (there is no value projection), so dv = dk.  The paged cache holds the normed keys and the raw keys (as values); a pooled cache beside it holds, page by
+    page, the means of the blocks that end in the page (csrc/attention_window.cu).
+
+    weights: q [H dk, D], k [G dk, D], o [D, H dk]; optional q.norm, k.norm [dk], pb [H].  window = 0: every earlier token is seen (and no pooled block)."""
+    kind = "kv"
+
+    def __init__(self, w: Dict[str, torch.Tensor], heads: int, kv_heads: int, dk: int, scale: float, eps: float, dtype: torch.dtype, window: int = 0, pool: int = 0,
+                 block_size: int = 64):
+        if heads % kv_heads:
+            raise BackendError("PooledWindowAttentionMixer: heads must be a multiple of kv_heads")
+        if tuple(w["q"].shape)[0] != heads * dk or tuple(w["k"].shape)[0] != kv_heads * dk or tuple(w["o"].shape)[1] != heads * dk:
+            raise BackendError(f"PooledWindowAttentionMixer: q {tuple(w['q'].shape)}, k {tuple(w['k'].shape)}, o {tuple(w['o'].shape)} for {heads} / {kv_heads} heads of {dk}")
+        self.H, self.G, self.dk, self.dv, self.scale, self.eps, self.dtype = heads, kv_heads, dk, dk, float(scale), eps, dtype
+        self.window, self.block_size = int(window), block_size
+        self.pool = int(pool) if self.window > 0 else 0
+        self.w_in = torch.cat([w["q"], w["k"]], 0).to(dtype).contiguous()
+        self.q_norm = w["q.norm"].float().contiguous() if "q.norm" in w else None
+        self.k_norm = w["k.norm"].float().contiguous() if "k.norm" in w else None
+        self.head_bias = w["pb"].float().contiguous() if "pb" in w else None
+        self.w_o = w["o"].to(dtype).contiguous()
+
+    def cache_shape(self):
+        return (self.G, self.dk, self.dk)
+
+    def pool_shape(self):
+        """(pooled entries per page, kv heads, key size, value size) of the f32 pooled cache, None without pooling"""
+        return (ops.pooled_entries_per_block(self.block_size, self.pool), self.G, self.dk, self.dk) if self.pool else None
+
+    def forward(self, h: torch.Tensor, batch: StepBatch, cache, proj: Optional[torch.Tensor] = None) -> torch.Tensor:
+        k_cache, v_cache = cache[0], cache[1]
+        k_pool, v_pool = (cache[2], cache[3]) if self.pool else (None, None)
+        if proj is None:
+            proj = ops.linear(h, self.w_in)
+        q = ops.qk_head_norm_rope_cache(proj, None, self.q_norm, self.k_norm, None, None, batch, k_cache, v_cache, self.H, self.G, self.dk, self.dk, 0, self.eps,
+                                        norm="before", v_from_k=True)
+        if self.pool:
+            ops.pooled_cache_update(k_cache, v_cache, k_pool, v_pool, batch, self.pool)
+        a = ops.paged_attention_sigmoid_pooled(q, k_cache, v_cache, k_pool, v_pool, batch, self.head_bias, self.H, self.scale, self.window, self.pool, self.dtype)
         return ops.linear(a, self.w_o)
 
 
@@ -170,6 +242,24 @@ class GatedMlp:
         return ops.linear(ops.glu_packed(proj, self.act, self.dtype), self.w_down)
 
 
+class UngatedMlp:
+    """down(act(up x)) with act = relu(.)^2; up [ff, D], down [D, ff]."""
+
+    def __init__(self, w: Dict[str, torch.Tensor], dtype: torch.dtype, act: str = "relu2"):
+        if act != "relu2":
+            raise BackendError(f"UngatedMlp: unknown activation {act!r}")
+        self.dtype, self.act = dtype, act
+        self.w_in = w["up"].to(dtype).contiguous()
+        self.w_down = w["down"].to(dtype).contiguous()
+        self.ff = self.w_in.shape[0]
+
+    def forward(self, h: torch.Tensor, proj: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """``proj``: the product of ``w_in`` with the input when the caller has it already (columns of a wider fused projection)"""
+        if proj is None:
+            proj = ops.linear(h, self.w_in)
+        return ops.linear(ops.glu_packed(proj, self.act, self.dtype), self.w_down)
+
+
 GROUPED_MIN_ROWS = 256        # token-choice pairs from which the expert products take 128-row tiles per expert (below: 32-row tiles, weights on the 128-row side)
 GROUPED_MIN_TOKENS = 16       # rows from which the latent up-projections run head by head on the tensor-core GEMM (each head's rows padded to 128)
 
@@ -181,17 +271,28 @@ class LatentAttentionMixer:
 
     weights: q [H (dn + rot_dim), D] (per head: dn unrotated then rot_dim rotated), dkv [rank + rot_dim, D] and dkv.norm [rank] (absent when
     ``shared``: the layer then attends over the cache another layer writes), uk [H dn, rank], uv [H dv, rank], o [D, H dv]; optional sink [H], g [H, D].
+    With ``q_rank`` the queries go through a latent of their own: dq [q_rank, D], dq.norm [q_rank], uq [H (dn + rot_dim), q_rank] take the place of q
+    (q = uq rms_norm(dq h)).  ``gate`` "element": g is [H dv, D], one sigmoid gate per output entry instead of one per head.
     rot = dict(base, scaling) or None (the rotation always spans the whole rot_dim part); window = 0 for none."""
     kind = "kv"
 
     def __init__(self, w: Dict[str, torch.Tensor], heads: int, dn: int, rot_dim: int, dv: int, rank: int, scale: float, eps: float, dtype: torch.dtype,
-                 rot: Optional[dict] = None, shared: bool = False, window: int = 0, block_size: int = 64, max_pos: int = 4096):
+                 rot: Optional[dict] = None, shared: bool = False, window: int = 0, block_size: int = 64, max_pos: int = 4096, q_rank: int = 0,
+                 gate: str = "head"):
         if rot_dim % 2:
             raise BackendError(f"LatentAttentionMixer: the rotated part has {rot_dim} entries, not an even number")
+        if gate not in ("head", "element"):
+            raise BackendError(f"LatentAttentionMixer: gate {gate!r} (head / element)")
         self.H, self.dn, self.dr, self.dv, self.R, self.scale, self.eps, self.dtype = heads, dn, rot_dim, dv, rank, float(scale), eps, dtype
         self.shared, self.window, self.block_size, self.rot = bool(shared), int(window), block_size, rot
-        parts = [w["q"]]
-        self.off_dkv = heads * (dn + rot_dim)
+        self.q_rank, self.gate_per_element = int(q_rank), gate == "element"
+        if self.q_rank:
+            if tuple(w["dq"].shape)[0] != self.q_rank or tuple(w["uq"].shape) != (heads * (dn + rot_dim), self.q_rank):
+                raise BackendError(f"LatentAttentionMixer: dq {tuple(w['dq'].shape)} / uq {tuple(w['uq'].shape)} for a query latent of {self.q_rank}")
+            self.q_norm = w["dq.norm"].float().contiguous() if "dq.norm" in w else torch.ones(self.q_rank, dtype=torch.float32, device=w["dq"].device)
+            self.w_uq = w["uq"].to(dtype).contiguous()
+        parts = [w["dq"] if self.q_rank else w["q"]]
+        self.off_dkv = self.q_rank if self.q_rank else heads * (dn + rot_dim)
         self.off_g = self.off_dkv
         if not shared:
             parts.append(w["dkv"])
@@ -200,7 +301,11 @@ class LatentAttentionMixer:
         if self.has_gate:
             parts.append(w["g"])
         self.w_in = torch.cat(parts, 0).to(dtype).contiguous()
-        want = {"q": (heads * (dn + rot_dim),), "uk": (heads * dn, rank), "uv": (heads * dv, rank), "o": (None, heads * dv)}
+        want = {"uk": (heads * dn, rank), "uv": (heads * dv, rank), "o": (None, heads * dv)}
+        if not self.q_rank:
+            want["q"] = (heads * (dn + rot_dim),)
+        if self.has_gate:
+            want["g"] = (heads * (dv if self.gate_per_element else 1),)
         if not shared:
             want["dkv"] = (rank + rot_dim,)
         for name, shape in want.items():
@@ -238,6 +343,9 @@ class LatentAttentionMixer:
         if not self.shared:
             ops.latent_kv_rope_cache(proj, self.off_dkv, self.c_norm, self.cos, self.sin, batch, c_cache, kr_cache, self.R, self.dr, self.eps)
         gate = proj[:, self.off_g:] if self.has_gate else None
+        if self.q_rank:
+            # the queries' own latent: normed in f32, then up to the heads; from here on `proj` holds q at column 0 like a direct projection
+            proj = ops.linear(ops.rms_norm_ex(proj[:, :self.q_rank], self.q_norm, self.eps, 0.0, self.dtype), self.w_uq)
         T = proj.shape[0]
         if self.grouped and T >= GROUPED_MIN_TOKENS:
             # head-major buffers, every head's rows padded to whole 128-row tiles; tile i belongs to head i // (tiles per head)
@@ -265,11 +373,11 @@ class LatentAttentionMixer:
                                             out=o16.transpose(0, 1)[:T])
             v_hm = torch.empty((self.H, Tp, self.dv), dtype=torch.float32, device=proj.device)
             ops.linear_grouped(o16.view(self.H * Tp, self.R), self.w_uv.view(self.H, self.dv, self.R), heads_of, v_hm.view(self.H * Tp, self.dv))
-            a = ops.latent_out_gate(v_hm.transpose(0, 1)[:T], None, gate, self.H, self.dv, self.R, self.dtype)
+            a = ops.latent_out_gate(v_hm.transpose(0, 1)[:T], None, gate, self.H, self.dv, self.R, self.dtype, self.gate_per_element)
         else:
             q_lat = ops.latent_q_absorb(proj, self.w_uk, self.cos, self.sin, batch, self.H, self.dn, self.dr, self.R)
             o_lat = ops.latent_attention_varlen(q_lat, c_cache, kr_cache, batch, self.sink, self.H, self.R, self.dr, self.block_size, self.scale, self.window)
-            a = ops.latent_out_gate(o_lat, self.w_uv, gate, self.H, self.dv, self.R, self.dtype)
+            a = ops.latent_out_gate(o_lat, self.w_uv, gate, self.H, self.dv, self.R, self.dtype, self.gate_per_element)
         return ops.linear(a, self.w_o)
 
 
@@ -281,12 +389,13 @@ class RoutedExperts:
 
     ``score`` "sigmoid" scores every output by itself; ``normalise`` False keeps the chosen scores as they are; ``weight_input`` feeds an expert its token
     times the score instead of scaling what the expert returns; ``act`` "clamped" is g' sigmoid(1.702 g') (u' + 1) with g' = min(g, limit), u' = clamp(u,
-    +-limit)."""
+    +-limit); ``act`` "relu2" makes the experts ungated, down(relu(up x)^2) with weights e<j>.up / e<j>.down only.  An optional router.b [N] is a bias of
+    the logits (it counts for the choice and for the weights; softmax scores normalised over the chosen = a softmax over the chosen logits)."""
 
     def __init__(self, w: Dict[str, torch.Tensor], experts: int, identity: int, top: int, scale: float, dtype: torch.dtype, groups: int = 0, keep: int = 0,
                  score: str = "softmax", normalise: bool = True, weight_input: bool = False, act: str = "silu", limit: float = 0.0):
         self.E, self.I, self.top, self.scale, self.groups, self.keep, self.dtype = experts, identity, top, float(scale), int(groups), int(keep), dtype
-        if score not in ("softmax", "sigmoid") or act not in ("silu", "clamped") or (weight_input and identity):
+        if score not in ("softmax", "sigmoid") or act not in ("silu", "clamped", "relu2") or (weight_input and identity):
             raise BackendError(f"RoutedExperts: score {score!r} / activation {act!r} / weighted input with identity experts")
         self.score, self.normalise, self.weight_input, self.act, self.limit = score, bool(normalise), bool(weight_input), act, float(limit)
         self.N = experts + identity
@@ -296,10 +405,12 @@ class RoutedExperts:
             raise BackendError(f"RoutedExperts: top {top} / groups {groups} / keep {keep} do not fit {self.N} router outputs")
         self.router = w["router"].to(dtype).contiguous()
         self.correction = w["correction"].float().contiguous() if "correction" in w else None
+        self.router_bias = w["router.b"].float().contiguous() if "router.b" in w else None
         self.w_gu = self.w_d = None
         self.ff = 0
         if experts:
-            self.w_gu = torch.stack([torch.cat([w[f"e{j}.gate"], w[f"e{j}.up"]], 0) for j in range(experts)], 0).to(dtype).contiguous()
+            first = (lambda j: w[f"e{j}.up"]) if act == "relu2" else (lambda j: torch.cat([w[f"e{j}.gate"], w[f"e{j}.up"]], 0))
+            self.w_gu = torch.stack([first(j) for j in range(experts)], 0).to(dtype).contiguous()
             self.w_d = torch.stack([w[f"e{j}.down"] for j in range(experts)], 0).to(dtype).contiguous()
             self.ff = self.w_d.shape[2]
         D = self.router.shape[1]
@@ -311,7 +422,7 @@ class RoutedExperts:
         it already (columns of a wider fused projection)"""
         if logits is None:
             logits = ops.linear(h, self.router)
-        ids, wts = ops.moe_route(logits, self.correction, self.top, self.groups, self.keep, self.scale, self.score, self.normalise)
+        ids, wts = ops.moe_route(logits, self.correction, self.top, self.groups, self.keep, self.scale, self.score, self.normalise, bias=self.router_bias)
         # a weight on the expert's input is applied to both of its first products (W (s h) = s W h), in f32, before the activation
         pre, post = (wts, None) if self.weight_input else (None, wts)
         if self.grouped:
@@ -320,7 +431,7 @@ class RoutedExperts:
             tile = 128 if h.shape[0] * self.top >= GROUPED_MIN_ROWS else 32
             pair_row, row_pair, tile_expert = ops.moe_sorted_rows(ids, self.E, tile)
             xg = ops.moe_gather_rows(h, row_pair, self.top)
-            gu = ops.linear_grouped(xg, self.w_gu, tile_expert, torch.empty((xg.shape[0], 2 * self.ff), dtype=torch.float32, device=h.device), tile)
+            gu = ops.linear_grouped(xg, self.w_gu, tile_expert, torch.empty((xg.shape[0], self.w_gu.shape[1]), dtype=torch.float32, device=h.device), tile)
             if self.act == "silu" and pre is None:
                 act = ops.silu_mul_packed(gu, torch.bfloat16)
             else:

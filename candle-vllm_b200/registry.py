@@ -26,7 +26,7 @@ def architecture_of(config: dict) -> str:
 
 
 # the source group (build.GROUPS) whose library alone serves an architecture, for a first start from a source-only checkout
-_BUILD_GROUP = {"Gobesun": "ragged", "Guvusun": "latent", "Panarax": "hybrid"}
+_BUILD_GROUP = {"Gobesun": "ragged", "Guvusun": "latent", "Panarax": "hybrid", "Dofevik": "window"}
 
 
 def build_group_of(path: str) -> str:
@@ -61,6 +61,11 @@ def _panarax(path, **kw):
     return PanaraxModel.from_pretrained(path, **kw)
 
 
+def _dofevik(path, **kw):
+    from .dofevik import DofevikModel
+    return DofevikModel.from_pretrained(path, **kw)
+
+
 def _llama(path, **kw):
     from .llama import load_dense_checkpoint
     return load_dense_checkpoint(path, **kw)
@@ -69,4 +74,5 @@ def _llama(path, **kw):
 register_model("Gobesun", _gobesun)
 register_model("Guvusun", _guvusun)
 register_model("Panarax", _panarax)
+register_model("Dofevik", _dofevik)
 register_model("LlamaForCausalLM", _llama)

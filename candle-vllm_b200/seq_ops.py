@@ -9,7 +9,7 @@ from __future__ import annotations
 
 import ctypes as C
 from dataclasses import dataclass
-from typing import Optional
+from typing import Optional, Sequence
 
 import numpy as np
 import torch
@@ -331,14 +331,17 @@ def latent_attention_varlen(q_lat: torch.Tensor, c_cache: torch.Tensor, kr_cache
     return out
 
 
-def latent_out_gate(src: torch.Tensor, w_uv: Optional[torch.Tensor], gate: Optional[torch.Tensor], heads: int, dv: int, rank: int, out_dtype: torch.dtype) -> torch.Tensor:
-    """sigmoid(gate[t, h]) * (w_uv[h] src[t, h]) -> [T, H dv]; src f32 [T, H, rank] of any token / head strides; w_uv None: src is [T, H, dv] already"""
+def latent_out_gate(src: torch.Tensor, w_uv: Optional[torch.Tensor], gate: Optional[torch.Tensor], heads: int, dv: int, rank: int, out_dtype: torch.dtype,
+                    gate_per_element: bool = False) -> torch.Tensor:
+    """sigmoid(gate[t, h]) * (w_uv[h] src[t, h]) -> [T, H dv]; src f32 [T, H, rank] of any token / head strides; w_uv None: src is [T, H, dv] already;
+    ``gate_per_element``: gate is [T, H dv], one per output entry"""
     T = src.shape[0]
     out = torch.empty((T, heads * dv), dtype=out_dtype, device=src.device)
     if src.dtype != torch.float32 or src.stride(2) != 1:
         raise BackendError("latent_out_gate: src is f32 with a contiguous last axis")
-    lib().latent_out_gate(_ptr(src), C.c_int64(src.stride(0)), C.c_int64(src.stride(1)), _ptr(w_uv), _ptr(gate),
-                          C.c_int64(0 if gate is None else (gate.stride(0) if T > 1 else max(heads, gate.stride(0)))), _ptr(out),
+    lib().latent_out_gate_ex(_ptr(src), C.c_int64(src.stride(0)), C.c_int64(src.stride(1)), _ptr(w_uv), _ptr(gate),
+                          C.c_int64(0 if gate is None else (gate.stride(0) if T > 1 else max(heads * (dv if gate_per_element else 1), gate.stride(0)))),
+                          C.c_int32(1 if gate_per_element else 0), _ptr(out),
                           C.c_int32(T), C.c_int32(heads), C.c_int32(dv), C.c_int32(rank), C.c_int32(_tag(w_uv.dtype) if w_uv is not None else _tag(out_dtype)),
                           C.c_int32(_tag(out_dtype)), _stream(src.device))
     check("latent_out_gate")
@@ -361,13 +364,13 @@ def linear_grouped(x: torch.Tensor, weight: torch.Tensor, tile_group: torch.Tens
 
 
 def moe_route(logits: torch.Tensor, correction: Optional[torch.Tensor], top: int, groups: int, keep: int, scale: float, score: str = "softmax",
-              normalise: bool = True):
+              normalise: bool = True, bias: Optional[torch.Tensor] = None):
     """f32 [T, N] -> (ids i32 [T, top], weights f32 [T, top]); ``score`` softmax over the outputs or a sigmoid per output; ``normalise`` False leaves the
-    chosen scores (times scale) as they are"""
+    chosen scores (times scale) as they are; ``bias`` (f32 [N]) is added to the logits first (``correction`` only to the scores the choice is made by)"""
     T, N = logits.shape
     ids = torch.empty((T, top), dtype=torch.int32, device=logits.device)
     w = torch.empty((T, top), dtype=torch.float32, device=logits.device)
-    lib().moe_route_ex(_ptr(logits), C.c_int64(logits.stride(0) if T > 1 else max(N, logits.stride(0))), _ptr(correction), _ptr(ids), _ptr(w), C.c_int32(T), C.c_int32(N),
+    lib().moe_route_bias(_ptr(logits), C.c_int64(logits.stride(0) if T > 1 else max(N, logits.stride(0))), _ptr(bias), _ptr(correction), _ptr(ids), _ptr(w), C.c_int32(T), C.c_int32(N),
                        C.c_int32(top), C.c_int32(groups), C.c_int32(keep), C.c_float(scale), C.c_int32({"softmax": 0, "sigmoid": 1}[score]), C.c_int32(1 if normalise else 0),
                        _stream(logits.device))
     check("moe_route")
@@ -381,9 +384,10 @@ def moe_gate_up(h: torch.Tensor, w_gate_up: torch.Tensor, ids: torch.Tensor, ord
     T, D = h.shape
     E, ff2, _ = w_gate_up.shape
     top = ids.shape[1]
-    out = torch.empty((T * top, ff2 // 2), dtype=h.dtype, device=h.device)
+    ff = ff2 if act == "relu2" else ff2 // 2            # ungated experts: w_gate_up is the one matrix [E, ff, D] in front of the activation
+    out = torch.empty((T * top, ff), dtype=h.dtype, device=h.device)
     lib().moe_gate_up_ex(_ptr(h), C.c_int64(h.stride(0) if T > 1 else max(D, h.stride(0))), _ptr(w_gate_up), _ptr(ids), _ptr(order), _ptr(out), C.c_int32(T), C.c_int32(top),
-                         C.c_int32(E), C.c_int32(ff2 // 2), C.c_int32(D), C.c_int32(GLU_ACTS[act]), C.c_float(limit), _ptr(pair_scale), C.c_int32(_tag(h.dtype)), _stream(h.device))
+                         C.c_int32(E), C.c_int32(ff), C.c_int32(D), C.c_int32(GLU_ACTS[act]), C.c_float(limit), _ptr(pair_scale), C.c_int32(_tag(h.dtype)), _stream(h.device))
     check("moe_gate_up")
     return out
 
@@ -550,15 +554,16 @@ def gated_residual_add(x: torch.Tensor, y: torch.Tensor, gate_logits: Optional[t
     return x
 
 
-GLU_ACTS = {"silu": 0, "gelu_tanh": 1, "clamped": 2}
+GLU_ACTS = {"silu": 0, "gelu_tanh": 1, "clamped": 2, "relu2": 3}      # "relu2" is ungated: relu(x)^2 from rows of ff entries
 
 
 def glu_packed(gate_up: torch.Tensor, act: str, out_dtype: torch.dtype, limit: float = 0.0, row_scale: Optional[torch.Tensor] = None,
                scale_index: Optional[torch.Tensor] = None) -> torch.Tensor:
     """act(gate) * up from f32 [rows, ff | ff]; ``row_scale`` (f32) first multiplies both halves of row r by row_scale[scale_index[r]] (or [r])"""
     rows, two_ff = gate_up.shape
-    out = torch.empty((rows, two_ff // 2), dtype=out_dtype, device=gate_up.device)
-    lib().glu_packed(_ptr(gate_up), _ptr(out), C.c_int64(rows), C.c_int32(two_ff // 2), C.c_int64(gate_up.stride(0) if rows > 1 else two_ff), C.c_int32(GLU_ACTS[act]),
+    ff = two_ff if act == "relu2" else two_ff // 2
+    out = torch.empty((rows, ff), dtype=out_dtype, device=gate_up.device)
+    lib().glu_packed(_ptr(gate_up), _ptr(out), C.c_int64(rows), C.c_int32(ff), C.c_int64(gate_up.stride(0) if rows > 1 else two_ff), C.c_int32(GLU_ACTS[act]),
                      C.c_float(limit), _ptr(row_scale), _ptr(scale_index), C.c_int32(_tag(out_dtype)), _stream(gate_up.device))
     check("glu_packed")
     return out
@@ -678,4 +683,97 @@ def linear_attention(proj: torch.Tensor, off_q: int, off_k: int, off_v: int, sta
                            C.c_int32(T), C.c_int32(batch.num_seqs), C.c_int32(1 if kernel == "step" else 0), C.c_int32(heads), C.c_int32(dk), C.c_int32(dv),
                            _stream(proj.device))
     check("linear_attention")
+    return out
+
+
+# ---- per-head q / k preparation, softmax sink, attention without softmax over a window plus pooled blocks, ungated experts, pre-norm sum ------
+
+def add_rms_norm(x: torch.Tensor, pending: Sequence[Optional[torch.Tensor]], weight: Optional[torch.Tensor], eps: float, out_dtype: Optional[torch.dtype] = None,
+                 row_index: Optional[torch.Tensor] = None) -> Optional[torch.Tensor]:
+    """The pre-norm step on the f32 stream x [T, n] (contiguous): x += sum of ``pending`` (up to two f32 tensors [T, n], row stride allowed) in place,
+    then rms_norm(x) * weight -> [T, n] of ``out_dtype``.  ``weight`` None: the sum alone (returns None).  ``row_index`` (i32 [R]): only those rows are
+    summed and normed ([R, n] comes back) and x is left as it is."""
+    T, n = x.shape
+    ys = [y for y in pending if y is not None]
+    if len(ys) > 2 or x.dtype != torch.float32 or not x.is_contiguous() or any(y.dtype != torch.float32 or y.stride(1) != 1 or y.shape != x.shape for y in ys):
+        raise BackendError("add_rms_norm: an f32 contiguous stream and at most two f32 addends of its shape")
+    if weight is None and (not ys or row_index is not None):
+        return None
+    ys += [None] * (2 - len(ys))
+    rows = T if row_index is None else row_index.shape[0]
+    out = None if weight is None else torch.empty((rows, n), dtype=out_dtype, device=x.device)
+    pitch = lambda t: 0 if t is None else (t.stride(0) if T > 1 else max(n, t.stride(0)))
+    lib().add_rms_norm(_ptr(x), _ptr(ys[0]), C.c_int64(pitch(ys[0])), _ptr(ys[1]), C.c_int64(pitch(ys[1])), _ptr(weight), _ptr(out), _ptr(row_index), C.c_int32(rows),
+                       C.c_int32(n), C.c_float(eps), C.c_int32(_tag(out_dtype) if out is not None else DType.F32), _stream(x.device))
+    check("add_rms_norm")
+    return out
+
+
+def qk_head_norm_rope_cache(proj: torch.Tensor, bias: Optional[torch.Tensor], q_norm: Optional[torch.Tensor], k_norm: Optional[torch.Tensor], cos: Optional[torch.Tensor],
+                            sin: Optional[torch.Tensor], batch: StepBatch, k_cache: torch.Tensor, v_cache: torch.Tensor, heads: int, kv_heads: int, dk: int, dv: int,
+                            rot_dims: int, eps: float, interleaved: bool = False, norm: str = "none", v_from_k: bool = False,
+                            q_dtype: torch.dtype = torch.float32) -> torch.Tensor:
+    """proj f32 [T, H dk | G dk | G dv] (+ bias f32 of that length): every q and k head normed over dk (``norm`` "before" / "after" the rotation / "none"; weights
+    [dk] shared by the heads or None), rotated on its first ``rot_dims`` entries (pairs (i, i + rot_dims/2) or, ``interleaved``, (2i, 2i + 1)); k and v go to the
+    paged cache, q [T, H dk] comes back.  ``v_from_k``: no value columns, the value is the key head as projected."""
+    T = proj.shape[0]
+    if cos is not None and batch.max_position >= cos.shape[0]:
+        raise BackendError(f"position {batch.max_position} is outside the rotary table ({cos.shape[0]} rows)")
+    q = torch.empty((T, heads * dk), dtype=q_dtype, device=proj.device)
+    lib().qk_head_norm_rope_cache(_ptr(proj), C.c_int64(proj.stride(0) if T > 1 else proj.shape[1]), _ptr(bias), _ptr(q_norm), _ptr(k_norm), _ptr(cos), _ptr(sin),
+                                  C.c_int32(0 if cos is None else cos.shape[0]), _ptr(batch.positions), _ptr(batch.slot_mapping), _ptr(q), _ptr(k_cache), _ptr(v_cache),
+                                  C.c_int32(T), C.c_int32(heads), C.c_int32(kv_heads), C.c_int32(dk), C.c_int32(dv), C.c_int32(rot_dims if cos is not None else 0),
+                                  C.c_int32(1 if interleaved else 0), C.c_int32({"none": 0, "before": 1, "after": 2}[norm]), C.c_int32(1 if v_from_k else 0), C.c_float(eps),
+                                  C.c_int32(_tag(k_cache.dtype)), C.c_int32(_tag(q_dtype)), _stream(proj.device))
+    check("qk_head_norm_rope_cache")
+    return q
+
+
+def paged_attention_varlen_sink(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, batch: StepBatch, heads: int, kv_heads: int, dk: int, dv: int,
+                                block_size: int, scale: float, chunk: int, window: int, sink: Optional[torch.Tensor], out_dtype: torch.dtype) -> torch.Tensor:
+    """``paged_attention_varlen`` with exp(sink[h]) (f32 [H]) in the softmax denominator of head h"""
+    T = q.shape[0]
+    out = torch.empty((T, heads * dv), dtype=out_dtype, device=q.device)
+    lib().paged_attention_varlen_sink(_ptr(out), _ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(batch.block_tables), C.c_int32(batch.block_tables.shape[1]),
+                                      _ptr(batch.token_seq), _ptr(batch.positions), _ptr(batch.cu_seqlens), _ptr(batch.cu_seqlens_k), C.c_int32(batch.num_seqs),
+                                      C.c_int32(T), C.c_int32(heads), C.c_int32(kv_heads), C.c_int32(dk), C.c_int32(dv), C.c_int32(block_size), C.c_float(scale),
+                                      C.c_int32(chunk), C.c_int32(window), _ptr(sink), C.c_int32(_tag(q.dtype)), C.c_int32(_tag(k_cache.dtype)), C.c_int32(_tag(out_dtype)),
+                                      _stream(q.device))
+    check("paged_attention_varlen_sink")
+    return out
+
+
+def pooled_entries_per_block(block_size: int, pool: int) -> int:
+    """pooled entries a page must hold: the blocks of ``pool`` positions whose last position falls into one page"""
+    return -(-block_size // pool)
+
+
+def pooled_cache_update(k_cache: torch.Tensor, v_cache: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, batch: StepBatch, pool: int) -> None:
+    """After the step's keys and values are in the cache: every row whose position closes a block of ``pool`` positions writes the block's mean key and mean value
+    (f32) into the pooled caches [nb, per_block, G, dk | dv]."""
+    nb, bs, G, dk = k_cache.shape
+    dv = v_cache.shape[3]
+    if k_pool.dtype != torch.float32 or v_pool.dtype != torch.float32 or k_pool.shape[0] != nb or k_pool.shape[2:] != (G, dk) or v_pool.shape[2:] != (G, dv):
+        raise BackendError(f"pooled_cache_update: pooled caches {tuple(k_pool.shape)} / {tuple(v_pool.shape)} beside {tuple(k_cache.shape)} / {tuple(v_cache.shape)}")
+    lib().pooled_cache_update(_ptr(k_cache), _ptr(v_cache), _ptr(k_pool), _ptr(v_pool), _ptr(batch.block_tables), C.c_int32(batch.block_tables.shape[1]), _ptr(batch.token_seq),
+                              _ptr(batch.positions), _ptr(batch.slot_mapping), C.c_int32(batch.tokens.shape[0]), C.c_int32(G), C.c_int32(dk), C.c_int32(dv), C.c_int32(bs),
+                              C.c_int32(pool), C.c_int32(k_pool.shape[1]), C.c_int32(_tag(k_cache.dtype)), _stream(k_cache.device))
+    check("pooled_cache_update")
+
+
+def paged_attention_sigmoid_pooled(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, k_pool: Optional[torch.Tensor], v_pool: Optional[torch.Tensor],
+                                   batch: StepBatch, head_bias: Optional[torch.Tensor], heads: int, scale: float, window: int, pool: int,
+                                   out_dtype: torch.dtype) -> torch.Tensor:
+    """out[t, h] = sum_j sigmoid(q . k_j scale + head_bias[h]) v_j over the window's tokens and the pooled entries of the blocks wholly before the window;
+    q f32 [T, H dk] -> [T, H dv]"""
+    T = q.shape[0]
+    nb, bs, G, dk = k_cache.shape
+    dv = v_cache.shape[3]
+    out = torch.empty((T, heads * dv), dtype=out_dtype, device=q.device)
+    lib().paged_attention_sigmoid_pooled(_ptr(out), _ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(k_pool), _ptr(v_pool), _ptr(batch.block_tables),
+                                         C.c_int32(batch.block_tables.shape[1]), _ptr(batch.token_seq), _ptr(batch.positions), _ptr(head_bias), C.c_int32(T), C.c_int32(heads),
+                                         C.c_int32(G), C.c_int32(dk), C.c_int32(dv), C.c_int32(bs), C.c_float(scale), C.c_int32(window), C.c_int32(pool if k_pool is not None else 0),
+                                         C.c_int32(0 if k_pool is None else k_pool.shape[1]), C.c_int32(_tag(q.dtype)), C.c_int32(_tag(k_cache.dtype)), C.c_int32(_tag(out_dtype)),
+                                         _stream(q.device))
+    check("paged_attention_sigmoid_pooled")
     return out

@@ -641,6 +641,46 @@ void moe_route_ex(const float* logits, int64_t ld, const float* correction, int3
 void moe_gate_up_ex(const void* h, int64_t ldh, const void* w_gate_up, const int32_t* ids, const int32_t* order, void* act, int32_t num_tokens, int32_t top,
                     int32_t num_experts, int32_t ff, int32_t width, int32_t act_fn, float limit, const float* pair_scale, int32_t dtype, int64_t stream);
 
+/* ---- per-head preparation, softmax sink, attention without softmax over a window plus pooled blocks, ungated experts, pre-norm sum ----------------
+ * qk_head_norm_rope_cache: proj f32 [T, ld] = packed q|k|v product [H dk | G dk | G dv] (no value columns when v_from_k), bias f32 of that length or
+ *   null.  Every q and k head: RMS norm over dk (norm_mode 1; weights f32 [dk] shared by the heads or null), rotation of the first rot_dims entries by
+ *   cos / sin f32 [max_pos, rot_dims / 2] (pairs (i, i + rot_dims/2), or (2i, 2i + 1) when interleaved), RMS norm after the rotation (norm_mode 2).
+ *   q_out [T, H dk] of q_dtype; K [nb, bs, G, dk] / V [nb, bs, G, dv] of cache_dtype at slot_mapping[t] (negative = no write).  v_from_k: the value
+ *   of a token is its key head as projected (plus bias), dv == dk.
+ * paged_attention_varlen_sink: paged_attention_varlen with sink f32 [H] (or null): exp(sink[h]) joins the softmax denominator of head h.
+ * pooled_cache_update: rows whose position closes a block of `pool` positions write the mean of the block's cached keys / values into the f32 pooled
+ *   caches [nb, per_block, G, dk | dv] (per_block >= ceil(block_size / pool)); entry of block b: page of its last position, index b - floor(page bs / pool).
+ * paged_attention_sigmoid_pooled: out[t, h] = sum_j sigmoid(q . k_j scale + head_bias[h]) v_j over the window's tokens (window 0 = all) and the pooled
+ *   entries of the blocks that end at or before position - window (pool 0 = none); q F32, caches F32 / BF16, out F32 / BF16.
+ * latent_out_gate_ex: latent_out_gate with gate_per_element = 1 for a gate f32 [T, H dv] (one per output entry).
+ * moe_route_bias: moe_route_ex with logit_bias f32 [N] (or null) added to the logits first.
+ * moe_gate_up_ex act_fn 3 / glu_packed act 3: ungated experts, act = relu(W_up h)^2 with w [E, ff, D] / rows of ff entries.
+ * add_rms_norm: x f32 [rows, n] contiguous, in place: x += y1 + y2 (f32, row pitches ld1 / ld2, each may be null), then out = rms_norm(x) * weight of
+ *   out_dtype (weight and out both null: the sum alone).  With row_index (i32 [rows]) only those rows are summed and normed, x stays as it is. */
+void qk_head_norm_rope_cache(const float* proj, int64_t ld, const float* bias, const float* q_norm_w, const float* k_norm_w, const float* cos_t,
+                             const float* sin_t, int32_t max_pos, const int32_t* positions, const int64_t* slot_mapping, void* q_out, void* key_cache,
+                             void* value_cache, int32_t num_tokens, int32_t num_heads, int32_t num_kv_heads, int32_t dk, int32_t dv, int32_t rot_dims,
+                             int32_t interleaved, int32_t norm_mode, int32_t v_from_k, float eps, int32_t cache_dtype, int32_t q_dtype, int64_t stream);
+void paged_attention_varlen_sink(void* out, const void* q, const void* key_cache, const void* value_cache, const int32_t* block_tables,
+                                 int32_t table_width, const int32_t* token_seq, const int32_t* positions, const int32_t* cu_seqlens_q,
+                                 const int32_t* cu_seqlens_k, int32_t num_seqs, int32_t num_tokens, int32_t num_heads, int32_t num_kv_heads, int32_t dk,
+                                 int32_t dv, int32_t block_size, float scale, int32_t chunk, int32_t window, const float* sink, int32_t q_dtype,
+                                 int32_t cache_dtype, int32_t out_dtype, int64_t stream);
+void pooled_cache_update(const void* key_cache, const void* value_cache, float* pooled_keys, float* pooled_values, const int32_t* block_tables,
+                         int32_t table_width, const int32_t* token_seq, const int32_t* positions, const int64_t* slot_mapping, int32_t num_tokens,
+                         int32_t num_kv_heads, int32_t dk, int32_t dv, int32_t block_size, int32_t pool, int32_t per_block, int32_t cache_dtype, int64_t stream);
+void paged_attention_sigmoid_pooled(void* out, const void* q, const void* key_cache, const void* value_cache, const float* pooled_keys, const float* pooled_values,
+                                    const int32_t* block_tables, int32_t table_width, const int32_t* token_seq, const int32_t* positions, const float* head_bias,
+                                    int32_t num_tokens, int32_t num_heads, int32_t num_kv_heads, int32_t dk, int32_t dv, int32_t block_size, float scale,
+                                    int32_t window, int32_t pool, int32_t per_block, int32_t q_dtype, int32_t cache_dtype, int32_t out_dtype, int64_t stream);
+void latent_out_gate_ex(const float* src, int64_t src_stride_token, int64_t src_stride_head, const void* w_uv, const float* gate, int64_t ld_gate,
+                        int32_t gate_per_element, void* out, int32_t num_tokens, int32_t num_heads, int32_t dv, int32_t rank, int32_t w_dtype, int32_t out_dtype,
+                        int64_t stream);
+void moe_route_bias(const float* logits, int64_t ld, const float* logit_bias, const float* correction, int32_t* ids, float* weights, int32_t num_tokens,
+                    int32_t num_outputs, int32_t top, int32_t groups, int32_t keep, float scale, int32_t score_fn, int32_t normalise, int64_t stream);
+void add_rms_norm(float* x, const float* y1, int64_t ld1, const float* y2, int64_t ld2, const float* weight, void* out, const int32_t* row_index, int32_t rows,
+                  int32_t n, float eps, int32_t out_dtype, int64_t stream);
+
 #ifdef __cplusplus
 }
 #endif
