@@ -49,10 +49,11 @@ def parse():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--cpu-seconds", type=float, default=20.0)
     ap.add_argument("--parity-steps", type=int, default=3, help="decode steps compared against a TP=1 engine before timing (0 = off)")
-    ap.add_argument("--arch", default="llama", choices=["llama", "gobesun", "guvusun", "panarax"],
+    ap.add_argument("--arch", default="llama", choices=["llama", "gobesun", "guvusun", "panarax", "dofevik"],
                     help="llama = the metric (default, unchanged).  gobesun = prefill / decode throughput of the Gobesun decoder at layer sizes of real "
                          "models (random weights), beside a dense bf16 Llama of equal width / heads / ff / depth, with a per-kernel roofline table; "
-                         "one JSON line, single GPU.  guvusun / panarax = the same for those decoders (panarax beside a Gobesun of equal width / heads / ff / depth).")
+                         "one JSON line, single GPU.  guvusun / panarax / dofevik = the same for those decoders (panarax beside a Gobesun, dofevik beside a Guvusun of "
+                         "equal size).")
     ap.add_argument("--arch-sizes", default="w2048,w4096")
     return ap.parse_args()
 
@@ -1261,10 +1262,250 @@ def run_panarax(args):
                       "gpu_launches": int(pkg.lib().b200_total_kernel_launches() - l0), "sizes": results}))
 
 
+# --arch dofevik: softmax attention with a sink, sigmoid attention over a window plus pooled blocks, latent attention, ungated routed experts beside a
+# shared one -- beside a Guvusun (latent attention with a sink + routed experts) of equal size
+# ------------------------------------------------------------------------------------------------
+DOFEVIK_SIZES = {
+    # width, heads / kv heads of 128, window, pool, latent sizes, experts x ff (top) + shared ff, layers (the three mixers in turn)
+    "w2048": dict(width=2048, heads=16, kv=4, window=1024, pool=16, dim=128, rot=64, vdim=128, rank=512, q_rank=768, experts=64, ff=1408, top=6, shared=2816,
+                  vocab=32000, layers=6),
+    "w4096": dict(width=4096, heads=32, kv=8, window=1024, pool=16, dim=128, rot=64, vdim=128, rank=512, q_rank=1536, experts=32, ff=2048, top=4, shared=4096,
+                  vocab=32000, layers=3),
+}
+
+
+def run_dofevik(args):
+    import torch
+    import candle_vllm_b200 as pkg
+    from candle_vllm_b200 import seq_ops as ops, synthetic as S
+    from candle_vllm_b200.engine import ModelRunner
+    from candle_vllm_b200.dofevik import DofevikConfig, DofevikModel
+    from candle_vllm_b200.guvusun import GuvusunConfig, GuvusunModel
+
+    torch.cuda.set_device(0)
+    dev = "cuda"
+    peaks = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json"))) if os.path.exists(os.path.join(ROOT, "MEASURED_PEAKS.json")) else \
+        {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "fallback": True}
+    HBM, TC = peaks["hbm_gbs"] * 1e9, peaks["bf16_tflops"] * 1e12
+    props = torch.cuda.get_device_properties(0)
+    F32 = props.multi_processor_count * 128 * 2 * 1.965e9           # nominal f32 multiply-add rate: the bound of 32-bit SIMT arithmetic
+    K, W = max(args.steps, 1), max(args.warmup, 3)
+    P, B, CTX, hd = 4096, 32, 2048, 128
+    bf = torch.bfloat16
+    l0 = pkg.lib().b200_total_kernel_launches()
+
+    def timed(fn, reps, warm=3):
+        for _ in range(warm):
+            fn()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(reps):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) / reps * 1e-3
+
+    names = ["linear", "linear_grouped", "rms_norm_ex", "add_rms_norm", "residual_rms_norm", "embedding_scaled", "embedding_bigram", "gelu_tanh_gather_mul",
+             "qk_head_norm_rope_cache", "pooled_cache_update", "paged_attention_varlen_sink", "paged_attention_sigmoid_pooled", "latent_kv_rope_cache",
+             "latent_q_absorb", "latent_attention_varlen", "latent_attention_decode", "latent_out_gate", "repack_heads", "token_tables", "moe_route", "moe_sorted_rows",
+             "moe_gather_rows", "moe_combine_rows", "moe_gate_up", "moe_down", "glu_packed", "silu_mul_packed"]
+
+    def measure(model, V):
+        """(prefill s, decode s per step incl. host, decode s per step device, {(tag, kernel): [s]})"""
+        blocks_per = -(-(CTX + K + W + 8) // 64)
+        runner = ModelRunner(model, B * blocks_per + P // 64 + 1, B + 1, 64, decode_graphs=True, max_blocks_per_seq=blocks_per)
+        toks = torch.randint(0, V, (P,), generator=torch.Generator().manual_seed(1)).tolist()
+
+        def prefill():
+            runner.admit(10 ** 6)
+            runner.execute([dict(seq_id=10 ** 6, tokens=toks, want=[P - 1])])
+            runner.release(10 ** 6)
+        pre = timed(prefill, 3, 2)
+        for i in range(B):
+            runner.admit(i)
+        for i in range(0, B, 4):
+            runner.execute([dict(seq_id=j, tokens=toks[:CTX], want=[]) for j in range(i, i + 4)])
+        step_entries = lambda: [dict(seq_id=j, tokens=[toks[j]], want=[0]) for j in range(B)]
+        dec = timed(lambda: runner.execute(step_entries()), K, W)
+        dec_dev = timed(runner._graphs[B].graph.replay, K, 3)
+        kern = {}
+        orig = {n: getattr(ops, n) for n in names}
+
+        def instrument(tag):
+            def wrap(n):
+                def f(*a, **k):
+                    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                    torch.cuda.synchronize(); e0.record()
+                    r = orig[n](*a, **k)
+                    e1.record(); torch.cuda.synchronize()
+                    key = n
+                    if n == "linear":
+                        key = f"linear[{a[1].shape[0]}x{a[1].shape[1]}]"
+                    elif n == "linear_grouped":
+                        key = f"linear_grouped[{a[1].shape[0]}x{a[1].shape[1]}x{a[1].shape[2]}]"
+                    elif n == "glu_packed":
+                        key = f"glu_packed[{a[0].shape[1]}]"
+                    kern.setdefault((tag, key), []).append(e0.elapsed_time(e1) * 1e-3)
+                    return r
+                return f
+            for n in names:
+                setattr(ops, n, wrap(n))
+        instrument("prefill")
+        prefill(); kern.clear(); prefill()
+        runner.decode_graphs = False
+        instrument("decode")
+        runner.execute(step_entries())
+        for k in [k for k in kern if k[0] == "decode"]:
+            kern.pop(k)
+        runner.execute(step_entries())
+        for n in names:
+            setattr(ops, n, orig[n])
+        del runner
+        torch.cuda.empty_cache()
+        return pre, dec, dec_dev, kern
+
+    sampler = ClockSampler(0); sampler.start()
+    results = {}
+    for name in [n for n in args.arch_sizes.split(",") if n in DOFEVIK_SIZES]:
+        z = DOFEVIK_SIZES[name]
+        D, H, G, Wn, Pl, dn, dr, dv, R, Rq = z["width"], z["heads"], z["kv"], z["window"], z["pool"], z["dim"], z["rot"], z["vdim"], z["rank"], z["q_rank"]
+        E, ff, top, sff, V, NL = z["experts"], z["ff"], z["top"], z["shared"], z["vocab"], z["layers"]
+        mlp = dict(experts=E, ff=ff, top=top, shared_ff=sff)
+        layers = []
+        for i in range(NL):
+            if i % 3 == 0:
+                layers.append(S.dofevik_pooled_layer(H, G, hd, window=Wn, pool=Pl, **mlp))
+            elif i % 3 == 1:
+                layers.append(S.dofevik_latent_layer(H, dn, dr, dv, R, Rq, window=Wn, base=1e6, **mlp))
+            else:
+                layers.append(S.dofevik_attention_layer(H, G, hd, hd, window=Wn, rot_dims=hd, base=1e6, factor=2.0, **mlp))
+        cfg = S.dofevik_config(D, V, layers)
+        model = DofevikModel(DofevikConfig.from_dict(cfg), S.dofevik_weights(cfg, 0), dtype=bf, block_size=64, max_pos=P + 64, device=dev)
+        d_pre, d_dec, d_dec_dev, d_kern = measure(model, V)
+        del model
+        torch.cuda.empty_cache()
+        # ---- Guvusun of equal width / heads / latent sizes / experts / depth (its experts are gated: three matrices each; no shared expert)
+        glayers = [S.guvusun_layer(H, dn, dr, dv, R, experts=E, ff=ff, top=top, router_scale=1.8, base=1e6) for _ in range(NL)]
+        gcfg = S.guvusun_config(D, V, glayers, bigram=dict(buckets=65521, mul_prev=8191, mul_cur=131))
+        gmodel = GuvusunModel(GuvusunConfig.from_dict(gcfg), S.guvusun_weights(gcfg, 0), dtype=bf, block_size=64, max_pos=P + 64, device=dev)
+        g_pre, g_dec, g_dec_dev, g_kern = measure(gmodel, V)
+        del gmodel
+        torch.cuda.empty_cache()
+        # ---- the like kernel of the two paged attentions: the tensor-core kernel as the chunk-masked softmax attention of Gobesun calls it (no sink, no pooled
+        # entries), same heads and window, one prompt of P rows and one step of B rows at context CTX
+        like = {}
+        g0 = torch.Generator().manual_seed(3)
+        nbp = P // 64 + 1
+        kc = (torch.randn(nbp, 64, G, hd, generator=g0) * 0.5).to(bf).to(dev)
+        vc = (torch.randn(nbp, 64, G, hd, generator=g0) * 0.5).to(bf).to(dev)
+        qq = (torch.randn(P, H * hd, generator=g0) * 0.1).to(bf).to(dev)
+        from candle_vllm_b200.inputs import prepare_step
+        bp = ops.StepBatch.from_host(prepare_step([dict(tokens=[0] * P, start=0, block_table=list(range(nbp)), state_slot=-1, want=[])], 64), dev)
+        like[("prefill", "paged_attention_varlen")] = [timed(lambda: ops.paged_attention_varlen(qq, kc, vc, bp, H, G, hd, hd, 64, hd ** -0.5, 0, Wn, bf), 3, 2)]
+        nbd = B * (CTX // 64 + 1)
+        kc = (torch.randn(nbd, 64, G, hd, generator=g0) * 0.5).to(bf).to(dev)
+        vc = (torch.randn(nbd, 64, G, hd, generator=g0) * 0.5).to(bf).to(dev)
+        per = CTX // 64 + 1
+        bd = ops.StepBatch.from_host(prepare_step([dict(tokens=[0], start=CTX, block_table=list(range(j * per, (j + 1) * per)), state_slot=-1, want=[]) for j in range(B)], 64), dev)
+        like[("decode", "paged_attention_varlen")] = [timed(lambda: ops.paged_attention_varlen(qq[:B], kc, vc, bd, H, G, hd, hd, 64, hd ** -0.5, 0, Wn, bf), 20, 3)]
+        del kc, vc, qq
+        torch.cuda.empty_cache()
+        med = lambda v: sorted(v)[len(v) // 2]
+        esz, Wd = 2, R + dr
+
+        def work(tag, key, T):
+            """algorithmic work of one call: ("bytes", n) against the measured copy bandwidth, ("flops", n) against the measured bf16 GEMM rate, ("f32", n)
+            against the nominal f32 multiply-add rate"""
+            pre = tag == "prefill"
+            if key.startswith("linear["):
+                n, k = (int(v) for v in key[7:-1].split("x"))
+                if n == V and pre:
+                    T = 1
+                return ("flops", 2.0 * T * n * k) if (pre and T > 1) else ("bytes", n * k * esz + T * (k * esz + n * 4))
+            if key.startswith("linear_grouped["):
+                g, n, k = (int(v) for v in key[15:-1].split("x"))
+                rows = T * top if g == E else T * H
+                return ("flops", 2.0 * rows * n * k) if pre else ("bytes", min(g, rows) * n * k * esz + rows * (k * esz + n * 4))
+            if key.startswith("glu_packed["):
+                n = int(key[11:-1])
+                return ("bytes", T * (top if n == ff else 1) * n * (4 + esz))
+            # keys a row sees: window tokens (all earlier ones while the context is shorter), plus pooled blocks wholly before the window
+            win = sum(min(i + 1, Wn) for i in range(T)) if pre else T * min(CTX + 1, Wn)
+            blk = sum(max(0, (i - Wn + 1) // Pl) for i in range(T)) if pre else T * max(0, (CTX - Wn + 1) // Pl)
+            full = T * (T + 1) / 2 if pre else T * (CTX + 1)
+            table = {
+                "rms_norm_ex": ("bytes", T * Rq * (4 + esz)), "add_rms_norm": ("bytes", T * D * (16 + esz)),
+                "residual_rms_norm": ("bytes", T * D * (12 + esz)), "embedding_scaled": ("bytes", T * D * (esz + 4)), "embedding_bigram": ("bytes", T * D * (2 * esz + 4)),
+                "qk_head_norm_rope_cache": ("bytes", T * ((H + 2 * G) * hd * 4 + H * hd * esz + 2 * G * hd * esz)),
+                "pooled_cache_update": ("bytes", (T / Pl) * 2 * G * hd * (Pl * esz + 4)),
+                "paged_attention_varlen_sink": ("flops", 4.0 * H * hd * win) if pre else ("bytes", win * 2 * G * hd * esz),
+                "paged_attention_varlen": ("flops", 4.0 * H * hd * win) if pre else ("bytes", win * 2 * G * hd * esz),
+                "paged_attention_sigmoid_pooled": ("flops", 4.0 * H * hd * (win + blk)) if pre else ("bytes", win * 2 * G * hd * esz + blk * 2 * G * hd * 4),
+                "latent_kv_rope_cache": ("bytes", T * Wd * (4 + esz)),
+                "latent_q_absorb": ("bytes", T * H * ((dn + dr) * 4 + Wd * 4 + (dn * esz if pre else 0)) + (0 if pre else H * dn * R * esz)),
+                "latent_out_gate": ("bytes", T * H * ((dv if pre else R) * 4 + dv * esz) + (0 if pre else H * dv * R * esz)),
+                "repack_heads": ("bytes", T * H * (R * 6 + R * 4 + dr * 6) / 3), "token_tables": ("bytes", T * ((CTX + K + W + 8) // 64 + 2) * 8),
+                "moe_route": ("bytes", T * (E * 4 + top * 8)), "moe_sorted_rows": ("bytes", T * top * 12),
+                "moe_gather_rows": ("bytes", T * top * D * esz * 2), "moe_combine_rows": ("bytes", T * top * D * 4 + T * D * 8),
+                "silu_mul_packed": ("bytes", T * top * ff * (8 + esz)),
+            }
+            return table.get(key)
+
+        def work_model(which, tag, key, T):
+            # latent attention: Dofevik's rows see a window (SIMT kernel over the latent cache), Guvusun's the whole context (split-KV tensor-core kernel);
+            # the expert matrices in front of the activation: one per expert (ungated) against two (gated)
+            pre = tag == "prefill"
+            win = sum(min(i + 1, Wn) for i in range(T)) if pre else T * min(CTX + 1, Wn)
+            full = T * (T + 1) / 2 if pre else T * (CTX + 1)
+            keys = win if which == "dofevik" else full
+            if key == "latent_attention_varlen":
+                return ("f32", keys * H * (2 * Wd + 2 * R)) if pre else ("bytes", keys * Wd * esz)
+            if key == "latent_attention_decode":
+                return ("flops", keys * H * (2 * Wd + 2 * R)) if pre else ("bytes", keys * Wd * esz * -(-H // 16))
+            if key == "moe_gate_up":
+                return ("bytes", min(T * top, E) * (1 if which == "dofevik" else 2) * ff * D * esz)
+            if key == "moe_down":
+                return ("bytes", min(T * top, E) * ff * D * esz)
+            return work(tag, key, T)
+
+        def table(which, kern, tag, T):
+            out = {}
+            for (tg, key), v in kern.items():
+                if tg != tag:
+                    continue
+                t = med(v)
+                e = {"us": round(t * 1e6, 1), "calls_per_step": len(v)}
+                w = work_model(which, tag, key, T)
+                if w:
+                    roof = w[1] / {"bytes": HBM, "flops": TC, "f32": F32}[w[0]]
+                    e.update(bound=w[0], roofline_us=round(roof * 1e6, 2), frac_of_roofline=round(roof / t, 3))
+                out[key] = e
+            return out
+        side = lambda which, pre, dec, dec_dev, kern: {
+            "prefill_tokens_per_s": round(P / pre), "prefill_ms": round(pre * 1e3, 2), "decode_tokens_per_s": round(B / dec), "decode_ms_per_step": round(dec * 1e3, 3),
+            "decode": "CUDA-graph replay incl. host metadata and H2D", "decode_ms_per_step_device": round(dec_dev * 1e3, 3),
+            "decode_tokens_per_s_device": round(B / dec_dev), "kernels_prefill": table(which, kern, "prefill", P), "kernels_decode": table(which, kern, "decode", B)}
+        results[name] = {"dofevik": side("dofevik", d_pre, d_dec, d_dec_dev, d_kern), "guvusun": side("guvusun", g_pre, g_dec, g_dec_dev, g_kern),
+                         "like_kernels": {"prefill": table("like", like, "prefill", P), "decode": table("like", like, "decode", B)},
+                         "shape": dict(z, prompt=P, decode_batch=B, decode_ctx=CTX, head_dim=hd)}
+    clocks = sampler.stop()
+    first = results[next(iter(results))]
+    print(json.dumps({"metric": "Dofevik prefill / decode tokens/s beside a Guvusun of equal size", "value": first["dofevik"]["decode_tokens_per_s"],
+                      "unit": UNIT, "n_gpus": 1, "steps": K, "warmup": W, "higher_is_better": True, "dtype": "bf16", "data": "synthetic", "arch": "dofevik",
+                      "peaks": {"hbm_gbs": peaks["hbm_gbs"], "bf16_tflops": peaks["bf16_tflops"], "f32_fma_tflops_nominal": round(F32 / 1e12, 1),
+                                "source": "fallback" if peaks.get("fallback") else "MEASURED_PEAKS.json"},
+                      "l2": "weights and activations of a step exceed L2 (126 MB)", "clocks": clocks,
+                      "gpu_launches": int(pkg.lib().b200_total_kernel_launches() - l0), "sizes": results}))
+
+
 def main():
     args = parse()
     if args.arch == "gobesun":
         run_gobesun(args)
+        return
+    if args.arch == "dofevik":
+        run_dofevik(args)
         return
     if args.arch == "panarax":
         run_panarax(args)

@@ -40,6 +40,7 @@ SYMBOLS = [
     "embedding_positional", "layer_norm_ex", "gated_residual_add", "gated_add_layer_norm", "glu_packed", "group_rms_norm_gate", "head_gate", "causal_conv_ex", "block_diag_linear", "gated_linear_scan",
     "linear_attention", "linear_attention_chunked", "linear_attention_chunked_scratch", "qk_norm_rope_cache_ex", "moe_route_ex", "moe_gate_up_ex",
     "qk_head_norm_rope_cache", "paged_attention_varlen_sink", "pooled_cache_update", "paged_attention_sigmoid_pooled", "latent_out_gate_ex", "moe_route_bias", "add_rms_norm",
+    "mla_paged_attention_window",
 ]
 
 
@@ -59,7 +60,7 @@ GROUP_SYMBOLS = {
                          "moe_align_rows", "moe_align", "moe_gather_rows", "silu_mul_packed", "moe_combine_rows"],
     "window": _COMMON + ["qk_head_norm_rope_cache", "paged_attention_varlen_sink", "pooled_cache_update", "paged_attention_sigmoid_pooled", "latent_kv_rope_cache",
                          "latent_q_absorb", "latent_attention_varlen", "latent_out_gate_ex", "repack_heads", "token_tables", "mla_decode_kernel_supported",
-                         "mla_paged_attention_sink", "mla_paged_decode_workspace_bytes", "moe_route_bias", "moe_gate_up_ex", "moe_down", "linear_grouped", "moe_align_rows",
+                         "mla_paged_attention_sink", "mla_paged_attention_window", "mla_paged_decode_workspace_bytes", "moe_route_bias", "moe_gate_up_ex", "moe_down", "linear_grouped", "moe_align_rows",
                          "moe_align", "moe_gather_rows", "moe_combine_rows"],
 }
 _RESTYPES = {"b200_last_error_message": C.c_char_p, "paged_attention_decode_workspace_bytes": C.c_size_t, "qmatmul_workspace_bytes": C.c_size_t,

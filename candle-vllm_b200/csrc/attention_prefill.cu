@@ -78,9 +78,17 @@ struct PrefillParams {
     int num_seqs, num_heads, num_kv_heads, max_blocks, window;
     int chunk;                      // > 0: a query at position i sees key j only if j / chunk == i / chunk
     float scale_log2;
+    const float* sink;              // [H] or null: the softmax denominator of head h also holds exp(sink[h]) (a key without a value, not scaled)
+    const float* head_bias;         // [H] or null (sigmoid mode): added to every score of head h
+    const float* kp; const float* vp;   // f32 pooled caches [nb, per_block, G, 128] or null: mean keys / values of blocks of `pool` positions
+    int pool, per_block;
 };
 
-template <typename T>
+// kSigmoid: the weight of a visible key is sigmoid(score * scale + head_bias[h]); no running maximum, no denominator.
+// With pooled caches, a row at position i also sees, like keys, the pooled entries of the blocks b with b pool + pool - 1 <= i - window; entry b lives
+// in the page of its last position at index b - floor(page 64 / pool).  Pooled tiles of 64 entries are gathered, converted to 16 bits and laid out
+// in shared memory like a page by all threads (the second stage buffer, before the page walk needs it), then take the same MMA path as a page.
+template <typename T, bool kSigmoid>
 __global__ void __launch_bounds__(kPfThreads, 2)
 paged_attn_prefill_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constant__ CUtensorMap vmap, const PrefillParams p) {
     extern __shared__ __align__(1024) uint8_t smem[];
@@ -149,11 +157,153 @@ paged_attn_prefill_kernel(const __grid_constant__ CUtensorMap kmap, const __grid
     float o[16][4];
 #pragma unroll
     for (int i = 0; i < 16; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
-    float m_lo = -INFINITY, m_hi = -INFINITY, l_lo = 0.f, l_hi = 0.f;
+    // with a sink the running maximum starts from it and the running sum from 1 (kept by one thread of the four that share a row)
+    const float sink_log2 = (!kSigmoid && p.sink) ? p.sink[head] * 1.4426950408889634f : -INFINITY;
+    float m_lo = sink_log2, m_hi = sink_log2, l_lo = (sink_log2 != -INFINITY && t == 0) ? 1.f : 0.f, l_hi = l_lo;
+    const float bias_log2 = (kSigmoid && p.head_bias) ? p.head_bias[head] * 1.4426950408889634f : 0.f;
     const int pos_lo = pos0 + r_lo, pos_hi = pos0 + r_hi;          // last visible key of each of this thread's two rows
     const int warp_min_pos = pos0 + warp * 16, warp_max_pos = pos0 + warp * 16 + 15;
     const int cs_lo = p.chunk > 0 ? (pos_lo / p.chunk) * p.chunk : 0, cs_hi = p.chunk > 0 ? (pos_hi / p.chunk) * p.chunk : 0;
     const int warp_min_cs = p.chunk > 0 ? (warp_min_pos / p.chunk) * p.chunk : 0, warp_max_cs = p.chunk > 0 ? (warp_max_pos / p.chunk) * p.chunk : 0;
+    // pooled blocks a row at position x sees: those that end at or before x - window
+    auto blocks_seen = [&](int x) { return (p.kp && p.pool > 0 && p.window > 0 && x - p.window + 1 > 0) ? (x - p.window + 1) / p.pool : 0; };
+    const int seen_lo = blocks_seen(pos_lo), seen_hi = blocks_seen(pos_hi);
+
+    // one 32-key half (a page's tokens, or pooled entries numbered from tok0): S = Q K^T, mask, weights, O += P V
+    auto process = [&](uint32_t kt, uint32_t vt, int tok0, bool pooled) {
+        // ---- S = Q K^T : 4 n-tiles (8 tokens) x 8 k-steps -----------------------------------------------------------------
+        float sacc[4][4];
+#pragma unroll
+        for (int nt = 0; nt < 4; ++nt) sacc[nt][0] = sacc[nt][1] = sacc[nt][2] = sacc[nt][3] = 0.f;
+#pragma unroll
+        for (int nt = 0; nt < 4; ++nt) {
+            const int row = nt * 8 + (lane & 7);
+#pragma unroll
+            for (int kp = 0; kp < 4; ++kp) {
+                const int chunk = kp * 4 + (lane >> 3);
+                uint32_t kb[4];
+                ldmatrix_x4(kb, kt + (chunk >> 3) * kSub + row * 128 + (((chunk & 7) ^ (row & 7)) << 4));
+                mma_16816<T>(sacc[nt], qa[2 * kp], kb[0], kb[1]);
+                mma_16816<T>(sacc[nt], qa[2 * kp + 1], kb[2], kb[3]);
+            }
+        }
+        // ---- mask (only where the half touches the diagonal / window edge / context end; always for pooled entries) -------------
+        const bool need_mask = pooled || tok0 + kHalf - 1 > warp_min_pos || (p.window > 0 && tok0 < warp_max_pos - p.window + 1) || tok0 < warp_max_cs;
+        float mx_lo = -INFINITY, mx_hi = -INFINITY;
+#pragma unroll
+        for (int nt = 0; nt < 4; ++nt) {
+#pragma unroll
+            for (int e = 0; e < 2; ++e) {
+                const int tok = tok0 + nt * 8 + 2 * t + e;
+                bool ok_lo = true, ok_hi = true;
+                if (pooled) {
+                    ok_lo = tok < seen_lo; ok_hi = tok < seen_hi;
+                } else if (need_mask) {
+                    ok_lo = tok <= pos_lo && (p.window <= 0 || tok > pos_lo - p.window) && tok >= cs_lo;
+                    ok_hi = tok <= pos_hi && (p.window <= 0 || tok > pos_hi - p.window) && tok >= cs_hi;
+                }
+                if constexpr (kSigmoid) {
+                    sacc[nt][e] = ok_lo ? 1.0f / (1.0f + fast_exp2(-(sacc[nt][e] * p.scale_log2 + bias_log2))) : 0.f;
+                    sacc[nt][2 + e] = ok_hi ? 1.0f / (1.0f + fast_exp2(-(sacc[nt][2 + e] * p.scale_log2 + bias_log2))) : 0.f;
+                } else {
+                    sacc[nt][e] = ok_lo ? sacc[nt][e] * p.scale_log2 : -INFINITY;
+                    sacc[nt][2 + e] = ok_hi ? sacc[nt][2 + e] * p.scale_log2 : -INFINITY;
+                    mx_lo = fmaxf(mx_lo, sacc[nt][e]);
+                    mx_hi = fmaxf(mx_hi, sacc[nt][2 + e]);
+                }
+            }
+        }
+        uint32_t pa[4][2];
+        if constexpr (kSigmoid) {
+#pragma unroll
+            for (int nt = 0; nt < 4; ++nt) { pa[nt][0] = pack2<T>(sacc[nt][0], sacc[nt][1]); pa[nt][1] = pack2<T>(sacc[nt][2], sacc[nt][3]); }
+        } else {
+            mx_lo = fmaxf(mx_lo, __shfl_xor_sync(0xffffffffu, mx_lo, 1)); mx_lo = fmaxf(mx_lo, __shfl_xor_sync(0xffffffffu, mx_lo, 2));
+            mx_hi = fmaxf(mx_hi, __shfl_xor_sync(0xffffffffu, mx_hi, 1)); mx_hi = fmaxf(mx_hi, __shfl_xor_sync(0xffffffffu, mx_hi, 2));
+            const float mn_lo = fmaxf(m_lo, mx_lo), mn_hi = fmaxf(m_hi, mx_hi);
+            // a row that has seen no visible key yet keeps m = -inf: use 0 as the subtrahend so that exp2(-inf - 0) = 0, never NaN
+            const float sub_lo = mn_lo == -INFINITY ? 0.f : mn_lo, sub_hi = mn_hi == -INFINITY ? 0.f : mn_hi;
+            const float c_lo = fast_exp2(m_lo - sub_lo), c_hi = fast_exp2(m_hi - sub_hi);
+            m_lo = mn_lo; m_hi = mn_hi;
+            l_lo *= c_lo; l_hi *= c_hi;
+#pragma unroll
+            for (int nt = 0; nt < 4; ++nt) {
+                const float p0 = fast_exp2(sacc[nt][0] - sub_lo), p1 = fast_exp2(sacc[nt][1] - sub_lo);
+                const float p2 = fast_exp2(sacc[nt][2] - sub_hi), p3 = fast_exp2(sacc[nt][3] - sub_hi);
+                l_lo += p0 + p1; l_hi += p2 + p3;
+                pa[nt][0] = pack2<T>(p0, p1); pa[nt][1] = pack2<T>(p2, p3);
+            }
+#pragma unroll
+            for (int i = 0; i < 16; ++i) { o[i][0] *= c_lo; o[i][1] *= c_lo; o[i][2] *= c_hi; o[i][3] *= c_hi; }
+        }
+        // ---- O += P V : 2 k-steps (16 tokens) x 16 n-tiles (8 dims).  V rows past the context hold whatever the block contains:
+        // their P is exactly 0 only if V is finite, so rows beyond klen are zeroed in shared memory first (as in the decode kernel);
+        // a pooled tile is built with zeros past its last entry
+        if (!pooled && tok0 + kHalf > klen) {
+            __syncwarp();
+            for (int r = max(klen - tok0, 0) + (lane >> 4); r < kHalf; r += 2) {
+                const int ch = lane & 15;
+                *reinterpret_cast<int4*>(smem + (vt - smem_base) + (ch >> 3) * kSub + r * 128 + (((ch & 7) ^ (r & 7)) << 4)) = make_int4(0, 0, 0, 0);
+            }
+            __syncwarp();
+        }
+#pragma unroll
+        for (int ktk = 0; ktk < 2; ++ktk) {
+            const uint32_t a[4] = {pa[2 * ktk][0], pa[2 * ktk][1], pa[2 * ktk + 1][0], pa[2 * ktk + 1][1]};
+            const int row = ktk * 16 + ((lane >> 3) & 1) * 8 + (lane & 7);
+#pragma unroll
+            for (int np = 0; np < 8; ++np) {
+                const int chunk = np * 2 + (lane >> 4);
+                uint32_t vb[4];
+                ldmatrix_x4_trans(vb, vt + (chunk >> 3) * kSub + row * 128 + (((chunk & 7) ^ (row & 7)) << 4));
+                mma_16816<T>(o[2 * np], a, vb[0], vb[1]);
+                mma_16816<T>(o[2 * np + 1], a, vb[2], vb[3]);
+            }
+        }
+    };
+
+    // ---- pooled entries first: tiles of 64 in the second stage buffer, which the page walk does not fill before its first iteration ---------------
+    const int seen_tile = blocks_seen(last_pos);
+    if (seen_tile > 0) {
+        const int warp_seen = blocks_seen(min(warp_max_pos, last_pos));
+        for (int b0 = 0; b0 < seen_tile; b0 += 64) {
+            {
+                const int e = threadIdx.x >> 1, part = threadIdx.x & 1;          // entry of the tile, and which 64 of its 128 entries
+                const int b = b0 + e, r = e & 31;
+                uint8_t* kdst = smem + kStage + (e >> 5) * 4 * kSub + part * kSub + r * 128;
+                uint8_t* vdst = kdst + 2 * kSub;
+                const float* ks = nullptr; const float* vs = nullptr;
+                if (b < seen_tile) {
+                    const int page = (b * p.pool + p.pool - 1) / kPg;
+                    const int64_t ent = (int64_t)table[page] * p.per_block + (b - (page * kPg) / p.pool);
+                    ks = p.kp + (ent * p.num_kv_heads + kvh) * kHd + part * 64;
+                    vs = p.vp + (ent * p.num_kv_heads + kvh) * kHd + part * 64;
+                }
+#pragma unroll
+                for (int c = 0; c < 8; ++c) {
+                    int4 kw = make_int4(0, 0, 0, 0), vw = make_int4(0, 0, 0, 0);
+                    if (ks) {
+                        const float4 k0 = reinterpret_cast<const float4*>(ks)[2 * c], k1 = reinterpret_cast<const float4*>(ks)[2 * c + 1];
+                        const float4 v0 = reinterpret_cast<const float4*>(vs)[2 * c], v1 = reinterpret_cast<const float4*>(vs)[2 * c + 1];
+                        kw = make_int4((int)pack2<T>(k0.x, k0.y), (int)pack2<T>(k0.z, k0.w), (int)pack2<T>(k1.x, k1.y), (int)pack2<T>(k1.z, k1.w));
+                        vw = make_int4((int)pack2<T>(v0.x, v0.y), (int)pack2<T>(v0.z, v0.w), (int)pack2<T>(v1.x, v1.y), (int)pack2<T>(v1.z, v1.w));
+                    }
+                    *reinterpret_cast<int4*>(kdst + ((c ^ (r & 7)) << 4)) = kw;
+                    *reinterpret_cast<int4*>(vdst + ((c ^ (r & 7)) << 4)) = vw;
+                }
+            }
+            __syncthreads();
+#pragma unroll 1
+            for (int h = 0; h < 2; ++h) {
+                if (b0 + h * kHalf >= warp_seen) break;
+                const uint32_t kt = smem_base + kStage + h * 4 * kSub;
+                process(kt, kt + 2 * kSub, b0 + h * kHalf, true);
+            }
+            __syncthreads();
+        }
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");           // the buffer goes back to the TMA loads of the page walk
+        __syncthreads();
+    }
 
     for (int page = page_lo, it = 0; page <= page_hi; ++page, ++it) {
         const int stage = it & 1;
@@ -165,91 +315,19 @@ paged_attn_prefill_kernel(const __grid_constant__ CUtensorMap kmap, const __grid
             if (tok0 > warp_max_pos) break;                          // entirely in the future of every row of this warp
             if (p.window > 0 && tok0 + kHalf - 1 < warp_min_pos - p.window + 1) continue;      // entirely before every row's window
             if (tok0 + kHalf - 1 < warp_min_cs) continue;                                      // entirely before every row's chunk
-            const uint32_t kt = smem_base + stage * kStage + h * 4 * kSub, vt = kt + 2 * kSub;
-            // ---- S = Q K^T : 4 n-tiles (8 tokens) x 8 k-steps -----------------------------------------------------------------
-            float sacc[4][4];
-#pragma unroll
-            for (int nt = 0; nt < 4; ++nt) sacc[nt][0] = sacc[nt][1] = sacc[nt][2] = sacc[nt][3] = 0.f;
-#pragma unroll
-            for (int nt = 0; nt < 4; ++nt) {
-                const int row = nt * 8 + (lane & 7);
-#pragma unroll
-                for (int kp = 0; kp < 4; ++kp) {
-                    const int chunk = kp * 4 + (lane >> 3);
-                    uint32_t kb[4];
-                    ldmatrix_x4(kb, kt + (chunk >> 3) * kSub + row * 128 + (((chunk & 7) ^ (row & 7)) << 4));
-                    mma_16816<T>(sacc[nt], qa[2 * kp], kb[0], kb[1]);
-                    mma_16816<T>(sacc[nt], qa[2 * kp + 1], kb[2], kb[3]);
-                }
-            }
-            // ---- mask (only where the half touches the diagonal / window edge / context end) + online softmax --------------------
-            const bool need_mask = tok0 + kHalf - 1 > warp_min_pos || (p.window > 0 && tok0 < warp_max_pos - p.window + 1) || tok0 < warp_max_cs;
-            float mx_lo = -INFINITY, mx_hi = -INFINITY;
-#pragma unroll
-            for (int nt = 0; nt < 4; ++nt) {
-#pragma unroll
-                for (int e = 0; e < 2; ++e) {
-                    const int tok = tok0 + nt * 8 + 2 * t + e;
-                    bool ok_lo = true, ok_hi = true;
-                    if (need_mask) {
-                        ok_lo = tok <= pos_lo && (p.window <= 0 || tok > pos_lo - p.window) && tok >= cs_lo;
-                        ok_hi = tok <= pos_hi && (p.window <= 0 || tok > pos_hi - p.window) && tok >= cs_hi;
-                    }
-                    sacc[nt][e] = ok_lo ? sacc[nt][e] * p.scale_log2 : -INFINITY;
-                    sacc[nt][2 + e] = ok_hi ? sacc[nt][2 + e] * p.scale_log2 : -INFINITY;
-                    mx_lo = fmaxf(mx_lo, sacc[nt][e]);
-                    mx_hi = fmaxf(mx_hi, sacc[nt][2 + e]);
-                }
-            }
-            mx_lo = fmaxf(mx_lo, __shfl_xor_sync(0xffffffffu, mx_lo, 1)); mx_lo = fmaxf(mx_lo, __shfl_xor_sync(0xffffffffu, mx_lo, 2));
-            mx_hi = fmaxf(mx_hi, __shfl_xor_sync(0xffffffffu, mx_hi, 1)); mx_hi = fmaxf(mx_hi, __shfl_xor_sync(0xffffffffu, mx_hi, 2));
-            const float mn_lo = fmaxf(m_lo, mx_lo), mn_hi = fmaxf(m_hi, mx_hi);
-            // a row that has seen no visible key yet keeps m = -inf: use 0 as the subtrahend so that exp2(-inf - 0) = 0, never NaN
-            const float sub_lo = mn_lo == -INFINITY ? 0.f : mn_lo, sub_hi = mn_hi == -INFINITY ? 0.f : mn_hi;
-            const float c_lo = fast_exp2(m_lo - sub_lo), c_hi = fast_exp2(m_hi - sub_hi);
-            m_lo = mn_lo; m_hi = mn_hi;
-            l_lo *= c_lo; l_hi *= c_hi;
-            uint32_t pa[4][2];
-#pragma unroll
-            for (int nt = 0; nt < 4; ++nt) {
-                const float p0 = fast_exp2(sacc[nt][0] - sub_lo), p1 = fast_exp2(sacc[nt][1] - sub_lo);
-                const float p2 = fast_exp2(sacc[nt][2] - sub_hi), p3 = fast_exp2(sacc[nt][3] - sub_hi);
-                l_lo += p0 + p1; l_hi += p2 + p3;
-                pa[nt][0] = pack2<T>(p0, p1); pa[nt][1] = pack2<T>(p2, p3);
-            }
-#pragma unroll
-            for (int i = 0; i < 16; ++i) { o[i][0] *= c_lo; o[i][1] *= c_lo; o[i][2] *= c_hi; o[i][3] *= c_hi; }
-            // ---- O += P V : 2 k-steps (16 tokens) x 16 n-tiles (8 dims).  V rows past the context hold whatever the block contains:
-            // their P is exactly 0 only if V is finite, so rows beyond klen are zeroed in shared memory first (as in the decode kernel)
-            if (tok0 + kHalf > klen) {
-                __syncwarp();
-                for (int r = max(klen - tok0, 0) + (lane >> 4); r < kHalf; r += 2) {
-                    const int ch = lane & 15;
-                    *reinterpret_cast<int4*>(smem + (vt - smem_base) + (ch >> 3) * kSub + r * 128 + (((ch & 7) ^ (r & 7)) << 4)) = make_int4(0, 0, 0, 0);
-                }
-                __syncwarp();
-            }
-#pragma unroll
-            for (int ktk = 0; ktk < 2; ++ktk) {
-                const uint32_t a[4] = {pa[2 * ktk][0], pa[2 * ktk][1], pa[2 * ktk + 1][0], pa[2 * ktk + 1][1]};
-                const int row = ktk * 16 + ((lane >> 3) & 1) * 8 + (lane & 7);
-#pragma unroll
-                for (int np = 0; np < 8; ++np) {
-                    const int chunk = np * 2 + (lane >> 4);
-                    uint32_t vb[4];
-                    ldmatrix_x4_trans(vb, vt + (chunk >> 3) * kSub + row * 128 + (((chunk & 7) ^ (row & 7)) << 4));
-                    mma_16816<T>(o[2 * np], a, vb[0], vb[1]);
-                    mma_16816<T>(o[2 * np + 1], a, vb[2], vb[3]);
-                }
-            }
+            const uint32_t kt = smem_base + stage * kStage + h * 4 * kSub;
+            process(kt, kt + 2 * kSub, tok0, false);
         }
         __syncthreads();                                             // every warp is done with this stage before it is refilled
     }
 
     // ---- normalise and store ------------------------------------------------------------------------------------------------------
-    l_lo += __shfl_xor_sync(0xffffffffu, l_lo, 1); l_lo += __shfl_xor_sync(0xffffffffu, l_lo, 2);
-    l_hi += __shfl_xor_sync(0xffffffffu, l_hi, 1); l_hi += __shfl_xor_sync(0xffffffffu, l_hi, 2);
-    const float inv_lo = l_lo > 0.f ? 1.f / l_lo : 0.f, inv_hi = l_hi > 0.f ? 1.f / l_hi : 0.f;
+    float inv_lo = 1.f, inv_hi = 1.f;
+    if constexpr (!kSigmoid) {
+        l_lo += __shfl_xor_sync(0xffffffffu, l_lo, 1); l_lo += __shfl_xor_sync(0xffffffffu, l_lo, 2);
+        l_hi += __shfl_xor_sync(0xffffffffu, l_hi, 1); l_hi += __shfl_xor_sync(0xffffffffu, l_hi, 2);
+        inv_lo = l_lo > 0.f ? 1.f / l_lo : 0.f; inv_hi = l_hi > 0.f ? 1.f / l_hi : 0.f;
+    }
     T* obase = static_cast<T*>(p.out);
 #pragma unroll
     for (int i = 0; i < 16; ++i) {
@@ -297,21 +375,25 @@ bool paged_attention_prefill_tc_supported(int head_dim, int block_size, int dtyp
 // DEVICE-side cu_seqlens, so a graph captured with padded metadata replays correctly)
 void paged_attention_prefill_tc(void* out, const void* q, const void* kc, const void* vc, const uint32_t* block_tables, const uint32_t* cu_q,
                                 const uint32_t* cu_k, int num_seqs, int total_q, int num_heads, int num_kv_heads, int max_blocks, int64_t num_blocks,
-                                float scale, int window, int dtype, cudaStream_t st, int chunk) {
+                                float scale, int window, int dtype, cudaStream_t st, int chunk, const PrefillExtras* extras) {
     CUtensorMap km, vm;
     if (!make_kv_map(&km, kc, num_blocks, num_kv_heads, dtype) || !make_kv_map(&vm, vc, num_blocks, num_kv_heads, dtype)) {
         set_error(kErrCuda, "paged_attention_prefill: cuTensorMapEncodeTiled failed");
         return;
     }
-    PrefillParams p{q, out, block_tables, cu_q, cu_k, num_seqs, num_heads, num_kv_heads, max_blocks, window, chunk, scale * 1.4426950408889634f};
-    const int tiles = total_q / kQTile + num_seqs;                   // >= sum of ceil(q_len / 64)
-    if (dtype == B200_BF16) {
-        ensure_dynamic_smem(reinterpret_cast<const void*>(paged_attn_prefill_kernel<__nv_bfloat16>), kPfSmem);
-        paged_attn_prefill_kernel<__nv_bfloat16><<<dim3(tiles, num_heads), kPfThreads, kPfSmem, st>>>(km, vm, p);
-    } else {
-        ensure_dynamic_smem(reinterpret_cast<const void*>(paged_attn_prefill_kernel<__half>), kPfSmem);
-        paged_attn_prefill_kernel<__half><<<dim3(tiles, num_heads), kPfThreads, kPfSmem, st>>>(km, vm, p);
+    PrefillParams p{q, out, block_tables, cu_q, cu_k, num_seqs, num_heads, num_kv_heads, max_blocks, window, chunk, scale * 1.4426950408889634f,
+                    nullptr, nullptr, nullptr, nullptr, 0, 0};
+    bool sigmoid = false;
+    if (extras) {
+        p.sink = extras->sink; p.head_bias = extras->head_bias; sigmoid = extras->sigmoid;
+        if (extras->pooled_keys && extras->pool > 0) { p.kp = extras->pooled_keys; p.vp = extras->pooled_values; p.pool = extras->pool; p.per_block = extras->per_block; }
     }
+    const int tiles = total_q / kQTile + num_seqs;                   // >= sum of ceil(q_len / 64)
+#define PF_LAUNCH(TT, SG) do { ensure_dynamic_smem(reinterpret_cast<const void*>(paged_attn_prefill_kernel<TT, SG>), kPfSmem); \
+        paged_attn_prefill_kernel<TT, SG><<<dim3(tiles, num_heads), kPfThreads, kPfSmem, st>>>(km, vm, p); } while (0)
+    if (dtype == B200_BF16) { if (sigmoid) PF_LAUNCH(__nv_bfloat16, true); else PF_LAUNCH(__nv_bfloat16, false); }
+    else { if (sigmoid) PF_LAUNCH(__half, true); else PF_LAUNCH(__half, false); }
+#undef PF_LAUNCH
     count_launch();
     check_launch("paged_attention_prefill");
 }

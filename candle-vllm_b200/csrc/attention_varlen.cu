@@ -244,11 +244,13 @@ void paged_attention_varlen_sink(void* out, const void* q, const void* key_cache
     // 16-bit q / cache / out with 128-wide heads and 64-token blocks: the tensor-core kernel that serves the other models' prefill
     // (attention_prefill.cu), with the chunk rule added to its mask; it covers portions and single tokens alike
     static const bool no_tc = [] { const char* e = getenv("B200_VARLEN_SIMT"); return e && atoi(e) != 0; }();
-    if (!no_tc && !sink && q_dtype == B200_BF16 && out_dtype == B200_BF16 && dk == dv && cu_seqlens_q && cu_seqlens_k && num_seqs > 0 &&
+    PrefillExtras extras;
+    extras.sink = sink;
+    if (!no_tc && q_dtype == B200_BF16 && out_dtype == B200_BF16 && dk == dv && cu_seqlens_q && cu_seqlens_k && num_seqs > 0 &&
         paged_attention_prefill_tc_supported(dk, block_size, B200_BF16, cache_dtype, B200_KV_FLASH, 0.f, 1, q, key_cache, value_cache)) {
         paged_attention_prefill_tc(out, q, key_cache, value_cache, (const uint32_t*)block_tables, (const uint32_t*)cu_seqlens_q,
                                    (const uint32_t*)cu_seqlens_k, num_seqs, num_tokens, num_heads, num_kv_heads, table_width, (int64_t)1 << 22, scale,
-                                   window, B200_BF16, st, chunk);
+                                   window, B200_BF16, st, chunk, &extras);
         return;
     }
     B200_REQUIRE(dv <= 32 * kMaxVPerLane && dk <= 2048, kErrUnsupported, "paged_attention_varlen: value size %d > %d or key size %d > 2048", dv,

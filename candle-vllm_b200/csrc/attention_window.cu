@@ -17,7 +17,11 @@
 //                            (0 <= i - j < window; window 0 = all) and, treated like tokens, the pooled entries of all blocks that end at or
 //                            before i - window.  Tokens that left the window whose block is not complete yet are not seen.  One warp per
 //                            (token, head): a lane scores one key, then the tile's values are accumulated with lanes across the value
-//                            columns; no normalisation over the keys.
+//                            columns; no normalisation over the keys.  With 16-bit q / cache / out, 128-wide heads and 64-token blocks the step runs on the
+//                            tensor-core kernel of attention_prefill.cu in its sigmoid form instead.
+#include <stdlib.h>
+
+#include "attention.cuh"
 #include "common.cuh"
 
 namespace b200 {
@@ -251,17 +255,30 @@ void pooled_cache_update(const void* key_cache, const void* value_cache, float* 
 }
 
 void paged_attention_sigmoid_pooled(void* out, const void* q, const void* key_cache, const void* value_cache, const float* pooled_keys, const float* pooled_values,
-                                    const int32_t* block_tables, int32_t table_width, const int32_t* token_seq, const int32_t* positions, const float* head_bias,
-                                    int32_t num_tokens, int32_t num_heads, int32_t num_kv_heads, int32_t dk, int32_t dv, int32_t block_size, float scale,
-                                    int32_t window, int32_t pool, int32_t per_block, int32_t q_dtype, int32_t cache_dtype, int32_t out_dtype, int64_t stream) {
+                                    const int32_t* block_tables, int32_t table_width, const int32_t* token_seq, const int32_t* positions, const int32_t* cu_seqlens_q,
+                                    const int32_t* cu_seqlens_k, int32_t num_seqs, const float* head_bias, int32_t num_tokens, int32_t num_heads, int32_t num_kv_heads,
+                                    int32_t dk, int32_t dv, int32_t block_size, float scale, int32_t window, int32_t pool, int32_t per_block, int32_t q_dtype,
+                                    int32_t cache_dtype, int32_t out_dtype, int64_t stream) {
     if (num_tokens == 0) return;
     B200_REQUIRE(out && q && key_cache && value_cache && block_tables && token_seq && positions, kErrBadArg, "paged_attention_sigmoid_pooled: null pointer");
     B200_REQUIRE(num_heads > 0 && num_kv_heads > 0 && num_heads % num_kv_heads == 0 && dk > 0 && dv > 0 && block_size > 0 && table_width > 0 && window >= 0 &&
                  pool >= 0 && (pool == 0 || (pooled_keys && pooled_values && per_block >= (block_size + pool - 1) / pool)), kErrBadArg,
                  "paged_attention_sigmoid_pooled: bad sizes");
+    cudaStream_t st = as_stream(stream);
+    // 16-bit q / cache / out with 128-wide heads and 64-token blocks: the tensor-core kernel of the softmax models in its sigmoid form (attention_prefill.cu);
+    // pooled entries are gathered into tiles of 64 and take the same MMA path as a page
+    static const bool no_tc = [] { const char* e = getenv("B200_VARLEN_SIMT"); return e && atoi(e) != 0; }();
+    if (!no_tc && q_dtype == B200_BF16 && out_dtype == B200_BF16 && dk == dv && cu_seqlens_q && cu_seqlens_k && num_seqs > 0 &&
+        paged_attention_prefill_tc_supported(dk, block_size, B200_BF16, cache_dtype, B200_KV_FLASH, 0.f, 1, q, key_cache, value_cache)) {
+        PrefillExtras extras;
+        extras.sigmoid = true; extras.head_bias = head_bias;
+        extras.pooled_keys = pooled_keys; extras.pooled_values = pooled_values; extras.pool = pool; extras.per_block = per_block;
+        paged_attention_prefill_tc(out, q, key_cache, value_cache, (const uint32_t*)block_tables, (const uint32_t*)cu_seqlens_q, (const uint32_t*)cu_seqlens_k,
+                                   num_seqs, num_tokens, num_heads, num_kv_heads, table_width, (int64_t)1 << 22, scale, window, B200_BF16, st, 0, &extras);
+        return;
+    }
     B200_REQUIRE(dv <= 32 * kMaxVPerLane && dk <= 2048, kErrUnsupported, "paged_attention_sigmoid_pooled: value size %d > %d or key size %d > 2048", dv,
                  32 * kMaxVPerLane, dk);
-    cudaStream_t st = as_stream(stream);
     const int64_t items = (int64_t)num_tokens * num_heads;
     const unsigned grid = (unsigned)((items + 3) / 4);
     const size_t smem = (size_t)4 * dk * sizeof(float);
@@ -271,6 +288,7 @@ void paged_attention_sigmoid_pooled(void* out, const void* q, const void* key_ca
     if (cache_dtype == B200_F32 && out_dtype == B200_F32 && q_dtype == B200_F32) PSP(float, float, float);
     else if (cache_dtype == B200_BF16 && out_dtype == B200_BF16 && q_dtype == B200_F32) PSP(__nv_bfloat16, __nv_bfloat16, float);
     else if (cache_dtype == B200_BF16 && out_dtype == B200_F32 && q_dtype == B200_F32) PSP(__nv_bfloat16, float, float);
+    else if (cache_dtype == B200_BF16 && out_dtype == B200_BF16 && q_dtype == B200_BF16) PSP(__nv_bfloat16, __nv_bfloat16, __nv_bfloat16);
     else { set_error(kErrUnsupported, "paged_attention_sigmoid_pooled: cache dtype %d / out dtype %d / q dtype %d", cache_dtype, out_dtype, q_dtype); return; }
 #undef PSP
     count_launch();

@@ -101,7 +101,11 @@ struct MlaParams {
     float* part_o; float* part_ml;             // [T][H][chunks][512], [T][H][chunks][2]
     int num_heads, max_blocks, max_chunks;
     float scale_log2;
+    int window;                                // > 0: a row sees only the last `window` keys of its context
 };
+
+// first key a row sees, rounded down to a whole tile: the chunks of a windowed row are counted from there (tiles never straddle a page)
+__device__ __forceinline__ int mla_first_key(int ctx, int window) { return window > 0 && ctx > window ? ctx - window : 0; }
 
 template <typename T>
 __global__ void __launch_bounds__(128, 2)
@@ -110,7 +114,8 @@ mla_decode_kernel(const __grid_constant__ CUtensorMap cmap, const __grid_constan
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
     const int chunk = blockIdx.x, seq = blockIdx.y, hg = blockIdx.z;
     const int ctx = (int)p.context_lens[seq];
-    const int tok_begin = chunk * kChunkTok;
+    const int first = mla_first_key(ctx, p.window);
+    const int tok_begin = (first & ~(kTl - 1)) + chunk * kChunkTok;
     if (tok_begin >= ctx) return;                                     // uniform per CTA
     const int ntok = min(kChunkTok, ctx - tok_begin), ntiles = (ntok + kTl - 1) / kTl;
     const uint32_t sb = smem_u32(smem);
@@ -182,8 +187,9 @@ mla_decode_kernel(const __grid_constant__ CUtensorMap cmap, const __grid_constan
         }
         // ---- mask, row maxima agreed across the four warps --------------------------------------------------------------------------
         const int tok = warp * 8 + 2 * t;
-        s[0] = tok < valid ? s[0] * p.scale_log2 : -INFINITY; s[1] = tok + 1 < valid ? s[1] * p.scale_log2 : -INFINITY;
-        s[2] = tok < valid ? s[2] * p.scale_log2 : -INFINITY; s[3] = tok + 1 < valid ? s[3] * p.scale_log2 : -INFINITY;
+        const int skip = first - (tok_begin + tl * kTl);             // tokens of this tile before the row's window (only the first tile of a windowed row has any)
+        s[0] = (tok < valid && tok >= skip) ? s[0] * p.scale_log2 : -INFINITY; s[1] = (tok + 1 < valid && tok + 1 >= skip) ? s[1] * p.scale_log2 : -INFINITY;
+        s[2] = (tok < valid && tok >= skip) ? s[2] * p.scale_log2 : -INFINITY; s[3] = (tok + 1 < valid && tok + 1 >= skip) ? s[3] * p.scale_log2 : -INFINITY;
         float mx_lo = fmaxf(s[0], s[1]), mx_hi = fmaxf(s[2], s[3]);
         mx_lo = fmaxf(mx_lo, __shfl_xor_sync(0xffffffffu, mx_lo, 1)); mx_lo = fmaxf(mx_lo, __shfl_xor_sync(0xffffffffu, mx_lo, 2));
         mx_hi = fmaxf(mx_hi, __shfl_xor_sync(0xffffffffu, mx_hi, 1)); mx_hi = fmaxf(mx_hi, __shfl_xor_sync(0xffffffffu, mx_hi, 2));
@@ -192,7 +198,7 @@ mla_decode_kernel(const __grid_constant__ CUtensorMap cmap, const __grid_constan
         float mn_lo = m_lo, mn_hi = m_hi;
 #pragma unroll
         for (int w = 0; w < 4; ++w) { mn_lo = fmaxf(mn_lo, wmax[w * kHg + g]); mn_hi = fmaxf(mn_hi, wmax[w * kHg + g + 8]); }
-        // every tile holds >= 1 valid token (token 0 of the tile, in warp 0), so the new maxima are finite
+        // every tile holds >= 1 valid token (its first one, or behind a window's edge its last ones), so the new maxima are finite
         const float c_lo = fast_exp2(m_lo - mn_lo), c_hi = fast_exp2(m_hi - mn_hi);
         m_lo = mn_lo; m_hi = mn_hi;
         const float p0 = fast_exp2(s[0] - mn_lo), p1 = fast_exp2(s[1] - mn_lo), p2 = fast_exp2(s[2] - mn_hi), p3 = fast_exp2(s[3] - mn_hi);
@@ -259,10 +265,10 @@ mla_decode_kernel(const __grid_constant__ CUtensorMap cmap, const __grid_constan
 template <typename T>
 __global__ void __launch_bounds__(128)
 mla_merge_kernel(T* __restrict__ out, const float* __restrict__ part_o, const float* __restrict__ part_ml, const uint32_t* __restrict__ context_lens,
-                 int num_heads, int max_chunks, const float* __restrict__ sink) {
+                 int num_heads, int max_chunks, const float* __restrict__ sink, int window) {
     const int head = blockIdx.x, seq = blockIdx.y;
     const int ctx = (int)context_lens[seq];
-    const int nchunks = (ctx + kChunkTok - 1) / kChunkTok;
+    const int nchunks = (ctx - (mla_first_key(ctx, window) & ~(kTl - 1)) + kChunkTok - 1) / kChunkTok;
     const int64_t base = ((int64_t)seq * num_heads + head) * max_chunks;
     // a softmax sink (one learned score per head, no key, no value) joins the maximum and the denominator here; the partial maxima are in
     // log2 units (scores were scaled by log2 e), the sink comes in natural units
@@ -404,6 +410,14 @@ void mla_paged_attention_sink(void* out, const void* q_absorbed, const void* q_p
                               const uint32_t* context_lens, const uint32_t* cu_seqlens_q, const float* sink, int32_t num_seqs, int32_t num_rows, int32_t num_heads,
                               int32_t kv_lora_rank, int32_t qk_rope_head_dim, int32_t block_size, int32_t max_blocks_per_seq, int64_t num_blocks, float sm_scale,
                               int32_t dtype, void* workspace, size_t workspace_bytes, int64_t stream) {
+    mla_paged_attention_window(out, q_absorbed, q_pe, ckv_cache, kpe_cache, block_tables, context_lens, cu_seqlens_q, sink, 0, num_seqs, num_rows, num_heads, kv_lora_rank,
+                               qk_rope_head_dim, block_size, max_blocks_per_seq, num_blocks, sm_scale, dtype, workspace, workspace_bytes, stream);
+}
+
+void mla_paged_attention_window(void* out, const void* q_absorbed, const void* q_pe, const void* ckv_cache, const void* kpe_cache, const uint32_t* block_tables,
+                                const uint32_t* context_lens, const uint32_t* cu_seqlens_q, const float* sink, int32_t window, int32_t num_seqs, int32_t num_rows,
+                                int32_t num_heads, int32_t kv_lora_rank, int32_t qk_rope_head_dim, int32_t block_size, int32_t max_blocks_per_seq, int64_t num_blocks,
+                                float sm_scale, int32_t dtype, void* workspace, size_t workspace_bytes, int64_t stream) {
     if (num_rows == 0 || num_seqs == 0) return;
     B200_REQUIRE(out && q_absorbed && q_pe && ckv_cache && kpe_cache && block_tables && context_lens, kErrBadArg, "mla_paged_attention: null pointer");
     B200_REQUIRE(dtype == B200_BF16 || dtype == B200_F16, kErrUnsupported, "mla_paged_attention: dtype %d (f16 / bf16)", dtype);
@@ -420,22 +434,23 @@ void mla_paged_attention_sink(void* out, const void* q_absorbed, const void* q_p
             const int max_chunks = (int)(((size_t)max_blocks_per_seq * block_size + kChunkTok - 1) / kChunkTok);
             MlaParams p{q_absorbed, q_pe, block_tables, context_lens, static_cast<float*>(workspace),
                         static_cast<float*>(workspace) + (size_t)num_seqs * num_heads * max_chunks * kLat, num_heads, max_blocks_per_seq, max_chunks,
-                        sm_scale * 1.4426950408889634f};
+                        sm_scale * 1.4426950408889634f, window > 0 ? window : 0};
             const dim3 grid(max_chunks, num_seqs, ceil_div(num_heads, kHg));
             if (dtype == B200_BF16) {
                 ensure_dynamic_smem(reinterpret_cast<const void*>(mla_decode_kernel<__nv_bfloat16>), kMlaSmem);
                 mla_decode_kernel<__nv_bfloat16><<<grid, 128, kMlaSmem, st>>>(cm, pm, p);
-                mla_merge_kernel<__nv_bfloat16><<<dim3(num_heads, num_seqs), 128, 0, st>>>((__nv_bfloat16*)out, p.part_o, p.part_ml, context_lens, num_heads, max_chunks, sink);
+                mla_merge_kernel<__nv_bfloat16><<<dim3(num_heads, num_seqs), 128, 0, st>>>((__nv_bfloat16*)out, p.part_o, p.part_ml, context_lens, num_heads, max_chunks, sink, p.window);
             } else {
                 ensure_dynamic_smem(reinterpret_cast<const void*>(mla_decode_kernel<__half>), kMlaSmem);
                 mla_decode_kernel<__half><<<grid, 128, kMlaSmem, st>>>(cm, pm, p);
-                mla_merge_kernel<__half><<<dim3(num_heads, num_seqs), 128, 0, st>>>((__half*)out, p.part_o, p.part_ml, context_lens, num_heads, max_chunks, sink);
+                mla_merge_kernel<__half><<<dim3(num_heads, num_seqs), 128, 0, st>>>((__half*)out, p.part_o, p.part_ml, context_lens, num_heads, max_chunks, sink, p.window);
             }
             count_launch(2);
             check_launch("mla_paged_attention");
             return;
         }
     }
+    B200_REQUIRE(window <= 0, kErrUnsupported, "mla_paged_attention_window: a window needs the split-KV decode kernel (latent 512, rope 64, 64-token blocks, one row per sequence)");
     B200_REQUIRE(!sink, kErrUnsupported, "mla_paged_attention_sink: a sink needs the split-KV decode kernel (latent 512, rope 64, 64-token blocks, one row per sequence)");
     const dim3 grid(num_heads, num_rows);
     if (dtype == B200_BF16)

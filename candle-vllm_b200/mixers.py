@@ -202,6 +202,8 @@ class PooledWindowAttentionMixer:
         self.k_norm = w["k.norm"].float().contiguous() if "k.norm" in w else None
         self.head_bias = w["pb"].float().contiguous() if "pb" in w else None
         self.w_o = w["o"].to(dtype).contiguous()
+        # 16-bit q for the tensor-core attention kernel (128-wide heads, 64-token blocks, bf16 cache); f32 q for the SIMT one
+        self.q_dtype = torch.bfloat16 if (dtype == torch.bfloat16 and dk == 128 and block_size == 64) else torch.float32
 
     def cache_shape(self):
         return (self.G, self.dk, self.dk)
@@ -216,7 +218,7 @@ class PooledWindowAttentionMixer:
         if proj is None:
             proj = ops.linear(h, self.w_in)
         q = ops.qk_head_norm_rope_cache(proj, None, self.q_norm, self.k_norm, None, None, batch, k_cache, v_cache, self.H, self.G, self.dk, self.dk, 0, self.eps,
-                                        norm="before", v_from_k=True)
+                                        norm="before", v_from_k=True, q_dtype=self.q_dtype)
         if self.pool:
             ops.pooled_cache_update(k_cache, v_cache, k_pool, v_pool, batch, self.pool)
         a = ops.paged_attention_sigmoid_pooled(q, k_cache, v_cache, k_pool, v_pool, batch, self.head_bias, self.H, self.scale, self.window, self.pool, self.dtype)
@@ -322,7 +324,7 @@ class LatentAttentionMixer:
         self.grouped = dtype == torch.bfloat16 and dn % 8 == 0 and rank % 8 == 0 and dn >= 64 and rank >= 64
         self.uk_t = self.w_uk.view(heads, dn, rank).transpose(1, 2).contiguous() if self.grouped else None
         self._tile_heads = {}
-        self.decode_kernel = self.grouped and self.window == 0 and ops.latent_decode_kernel_supported(rank, rot_dim, block_size, dtype)
+        self.decode_kernel = self.grouped and ops.latent_decode_kernel_supported(rank, rot_dim, block_size, dtype)
         self.cos = self.sin = None
         self._device = self.w_in.device
         if rot and rot_dim:
@@ -367,7 +369,7 @@ class LatentAttentionMixer:
                 qa = ops.repack_heads(q_lat[:T, :, :self.R], torch.empty((T, self.H, self.R), dtype=torch.bfloat16, device=proj.device))
                 qr = ops.repack_heads(q_lat[:T, :, self.R:], torch.empty((T, self.H, self.dr), dtype=torch.bfloat16, device=proj.device))
                 tables, ctx = ops.token_tables(batch)
-                ops.repack_heads(ops.latent_attention_decode(qa, qr, c_cache, kr_cache, tables, ctx, self.sink, self.scale), o16.transpose(0, 1)[:T])
+                ops.repack_heads(ops.latent_attention_decode(qa, qr, c_cache, kr_cache, tables, ctx, self.sink, self.scale, self.window), o16.transpose(0, 1)[:T])
             else:
                 ops.latent_attention_varlen(q_lat[:T], c_cache, kr_cache, batch, self.sink, self.H, self.R, self.dr, self.block_size, self.scale, self.window,
                                             out=o16.transpose(0, 1)[:T])

@@ -474,10 +474,11 @@ LATENT_DECODE_WORKSPACE = 1 << 31      # bytes of partials one call of the split
 
 
 def latent_attention_decode(q_abs: torch.Tensor, q_rot: torch.Tensor, c_cache: torch.Tensor, kr_cache: torch.Tensor, tables: torch.Tensor, context_lens: torch.Tensor,
-                            sink: Optional[torch.Tensor], scale: float) -> torch.Tensor:
+                            sink: Optional[torch.Tensor], scale: float, window: int = 0) -> torch.Tensor:
     """Rows as one-row sequences (``token_tables``) on the split-KV tensor-core kernel of the latent cache (csrc/mla.cu: TMA tiles, 16 heads per MMA,
     runs of 256 keys folded by a merge kernel that also takes the sink): q_abs bf16 [T, H, 512], q_rot bf16 [T, H, 64], bf16 caches of 64-token
-    blocks -> bf16 [T, H, 512].  Serves single decoded tokens and rows of prompts alike (each row has its own context length)."""
+    blocks -> bf16 [T, H, 512].  Serves single decoded tokens and rows of prompts alike (each row has its own context length); ``window`` > 0: a row sees
+    only the last ``window`` keys of its context."""
     T, H, R = q_abs.shape
     W = tables.shape[1]
     bs = c_cache.shape[1]
@@ -489,8 +490,8 @@ def latent_attention_decode(q_abs: torch.Tensor, q_rot: torch.Tensor, c_cache: t
     ws = torch.empty(need, dtype=torch.uint8, device=q_abs.device)
     for r0 in range(0, T, slab):
         n = min(slab, T - r0)
-        L.mla_paged_attention_sink(_ptr(out[r0:]), _ptr(q_abs[r0:]), _ptr(q_rot[r0:]), _ptr(c_cache), _ptr(kr_cache), _ptr(tables[r0:]), _ptr(context_lens[r0:]), _ptr(None),
-                                   _ptr(sink), C.c_int32(n), C.c_int32(n), C.c_int32(H), C.c_int32(R), C.c_int32(q_rot.shape[2]), C.c_int32(bs), C.c_int32(W),
+        L.mla_paged_attention_window(_ptr(out[r0:]), _ptr(q_abs[r0:]), _ptr(q_rot[r0:]), _ptr(c_cache), _ptr(kr_cache), _ptr(tables[r0:]), _ptr(context_lens[r0:]), _ptr(None),
+                                   _ptr(sink), C.c_int32(window), C.c_int32(n), C.c_int32(n), C.c_int32(H), C.c_int32(R), C.c_int32(q_rot.shape[2]), C.c_int32(bs), C.c_int32(W),
                                    C.c_int64(c_cache.shape[0]), C.c_float(scale), C.c_int32(DType.BF16), _ptr(ws), C.c_size_t(need), _stream(q_abs.device))
         check("latent_attention_decode")
     return out
@@ -748,6 +749,13 @@ def pooled_entries_per_block(block_size: int, pool: int) -> int:
     return -(-block_size // pool)
 
 
+def pooled_entry_location(block: int, pool: int, block_size: int):
+    """(page of the sequence, index inside the page) of the pooled entry of block ``block`` (positions block * pool .. block * pool + pool - 1): the page that
+    holds the block's last position, and the block's rank among the blocks that end in that page.  The kernels compute the same."""
+    page = (block * pool + pool - 1) // block_size
+    return page, block - (page * block_size) // pool
+
+
 def pooled_cache_update(k_cache: torch.Tensor, v_cache: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, batch: StepBatch, pool: int) -> None:
     """After the step's keys and values are in the cache: every row whose position closes a block of ``pool`` positions writes the block's mean key and mean value
     (f32) into the pooled caches [nb, per_block, G, dk | dv]."""
@@ -765,13 +773,14 @@ def paged_attention_sigmoid_pooled(q: torch.Tensor, k_cache: torch.Tensor, v_cac
                                    batch: StepBatch, head_bias: Optional[torch.Tensor], heads: int, scale: float, window: int, pool: int,
                                    out_dtype: torch.dtype) -> torch.Tensor:
     """out[t, h] = sum_j sigmoid(q . k_j scale + head_bias[h]) v_j over the window's tokens and the pooled entries of the blocks wholly before the window;
-    q f32 [T, H dk] -> [T, H dv]"""
+    q f32 [T, H dk] -> [T, H dv]; a bf16 q (128-wide heads, 64-token blocks, bf16 cache and output) takes the tensor-core kernel"""
     T = q.shape[0]
     nb, bs, G, dk = k_cache.shape
     dv = v_cache.shape[3]
     out = torch.empty((T, heads * dv), dtype=out_dtype, device=q.device)
     lib().paged_attention_sigmoid_pooled(_ptr(out), _ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(k_pool), _ptr(v_pool), _ptr(batch.block_tables),
-                                         C.c_int32(batch.block_tables.shape[1]), _ptr(batch.token_seq), _ptr(batch.positions), _ptr(head_bias), C.c_int32(T), C.c_int32(heads),
+                                         C.c_int32(batch.block_tables.shape[1]), _ptr(batch.token_seq), _ptr(batch.positions), _ptr(batch.cu_seqlens), _ptr(batch.cu_seqlens_k),
+                                         C.c_int32(batch.num_seqs), _ptr(head_bias), C.c_int32(T), C.c_int32(heads),
                                          C.c_int32(G), C.c_int32(dk), C.c_int32(dv), C.c_int32(bs), C.c_float(scale), C.c_int32(window), C.c_int32(pool if k_pool is not None else 0),
                                          C.c_int32(0 if k_pool is None else k_pool.shape[1]), C.c_int32(_tag(q.dtype)), C.c_int32(_tag(k_cache.dtype)), C.c_int32(_tag(out_dtype)),
                                          _stream(q.device))

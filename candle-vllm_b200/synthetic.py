@@ -416,3 +416,95 @@ def panarax_weights(cfg: dict, seed: int = 0, device="cpu") -> dict:
                 for j in range(E):
                     out[p + f"mlp.e{j}.gate"], out[p + f"mlp.e{j}.up"], out[p + f"mlp.e{j}.down"] = lin(ff, D) * 2.0, lin(ff, D) * 2.0, lin(D, ff)
     return {k: v.to(torch.bfloat16).to(device) for k, v in out.items()}
+
+
+# ---------------------------------------------------------------------------------------------------------------------
+# Dofevik: random checkpoints of any shape (tests and bench.py)
+# ---------------------------------------------------------------------------------------------------------------------
+def _dofevik_mlp(experts: int, ff: int, top: int, shared_ff: int):
+    if not experts:
+        return None
+    mlp = dict(kind="moe", expert=dict(ff=ff), router=dict(experts=experts, top=top))
+    if shared_ff:
+        mlp["shared"] = dict(ff=shared_ff)
+    return mlp
+
+
+def dofevik_attention_layer(heads: int, kv_heads: int, dim: int, vdim: int, window: int = 0, rot_dims: int = 0, base: float = 10000.0, factor: float = 0.0,
+                            scale: float = None, experts: int = 0, ff: int = 0, top: int = 1, shared_ff: int = 0) -> dict:
+    mixer = dict(heads=heads, kv_heads=kv_heads, dim=dim, vdim=vdim, scale=dim ** -0.5 if scale is None else scale)
+    if window:
+        mixer["mask"] = dict(size=window)
+    if rot_dims:
+        mixer["rot"] = dict(base=base, dims=rot_dims)
+        if factor:
+            mixer["rot"]["scaling"] = dict(factor=factor)
+    return dict(type="attention", mixer=mixer, mlp=_dofevik_mlp(experts, ff, top, shared_ff))
+
+
+def dofevik_pooled_layer(heads: int, kv_heads: int, dim: int, window: int = 0, pool: int = 0, scale: float = None, experts: int = 0, ff: int = 0, top: int = 1,
+                         shared_ff: int = 0) -> dict:
+    mixer = dict(heads=heads, kv_heads=kv_heads, dim=dim, vdim=dim, scale=dim ** -0.5 if scale is None else scale)
+    if window:
+        mixer["mask"] = dict(size=window)
+        if pool:
+            mixer["mask"]["pool"] = pool
+    return dict(type="attention_2", mixer=mixer, mlp=_dofevik_mlp(experts, ff, top, shared_ff))
+
+
+def dofevik_latent_layer(heads: int, dim: int, rot_dim: int, vdim: int, kv_rank: int, q_rank: int, window: int = 0, base: float = 10000.0, scale: float = None,
+                         experts: int = 0, ff: int = 0, top: int = 1, shared_ff: int = 0) -> dict:
+    mixer = dict(heads=heads, dim=dim, rot_dim=rot_dim, vdim=vdim, kv_rank=kv_rank, q_rank=q_rank, rot=dict(base=base, dims=rot_dim),
+                 scale=(dim + rot_dim) ** -0.5 if scale is None else scale)
+    if window:
+        mixer["mask"] = dict(size=window)
+    return dict(type="latent_attention", mixer=mixer, mlp=_dofevik_mlp(experts, ff, top, shared_ff))
+
+
+def dofevik_config(width: int, vocab: int, layers: list, eps: float = 1e-6) -> dict:
+    return dict(architecture="Dofevik", layers=layers, norm=dict(eps=eps), vocab=vocab, width=width)
+
+
+def dofevik_weights(cfg: dict, seed: int = 0, device="cpu") -> dict:
+    """name -> bf16 tensor with magnitudes that keep every mechanism visible in the logits: sinks of the order of the scores, sigmoid biases that leave the
+    weights away from 0 and 1, router biases large enough to change the choice, a peaked router, norm numbers away from one."""
+    g = torch.Generator().manual_seed(seed)
+    D, V = cfg["width"], cfg["vocab"]
+    out = {}
+    rnd = lambda *shape, std=1.0: (torch.randn(*shape, generator=g) * std)
+    lin = lambda n, k, gain=1.0: rnd(n, k, std=gain * k ** -0.5)
+    one = lambda: (0.7 + torch.rand((), generator=g) * 0.8)
+    out["embed"], out["head"], out["final.norm"] = rnd(V, D), lin(V, D), one()
+    for i, L in enumerate(cfg["layers"]):
+        p, m = f"l{i}.", L["mixer"]
+        out[p + "norm1"] = one()
+        H = m["heads"]
+        if L["type"] == "attention":
+            G, dk, dv = m["kv_heads"], m["dim"], m["vdim"]
+            out[p + "mix.q"], out[p + "mix.k"], out[p + "mix.v"] = lin(H * dk, D), lin(G * dk, D), lin(G * dv, D)
+            out[p + "mix.q.b"], out[p + "mix.k.b"], out[p + "mix.v.b"] = rnd(H * dk, std=0.3), rnd(G * dk, std=0.3), rnd(G * dv, std=0.3)
+            out[p + "mix.sink"] = rnd(H, std=1.5) + 1.0
+            out[p + "mix.o"] = lin(D, H * dv)
+        elif L["type"] == "attention_2":
+            G, dk = m["kv_heads"], m["dim"]
+            out[p + "mix.q"], out[p + "mix.k"] = lin(H * dk, D), lin(G * dk, D)
+            out[p + "mix.q.norm"], out[p + "mix.k.norm"] = 1.0 + rnd(dk, std=0.3), 1.0 + rnd(dk, std=0.3)
+            out[p + "mix.pb"] = rnd(H, std=0.8) - 2.0
+            out[p + "mix.o"] = lin(D, H * dk, 0.5)
+        else:
+            dn, dr, dv, R, Rq = m["dim"], m["rot_dim"], m["vdim"], m["kv_rank"], m["q_rank"]
+            out[p + "mix.dq"], out[p + "mix.dq.norm"], out[p + "mix.uq"] = lin(Rq, D), 1.0 + rnd(Rq, std=0.3), lin(H * (dn + dr), Rq, 1.5)
+            out[p + "mix.dkv"], out[p + "mix.dkv.norm"] = lin(R + dr, D), 1.0 + rnd(R, std=0.3)
+            out[p + "mix.uk"], out[p + "mix.uv"] = lin(H * dn, R, 1.5), lin(H * dv, R)
+            out[p + "mix.g"] = lin(H * dv, D, 2.0)
+            out[p + "mix.o"] = lin(D, H * dv)
+        if L.get("mlp"):
+            r, ff = L["mlp"]["router"], L["mlp"]["expert"]["ff"]
+            out[p + "norm2"] = one()
+            out[p + "mlp.router"], out[p + "mlp.router.b"] = lin(r["experts"], D, 3.0), rnd(r["experts"], std=1.0)
+            for j in range(r["experts"]):
+                out[p + f"mlp.e{j}.up"], out[p + f"mlp.e{j}.down"] = lin(ff, D), lin(D, ff)
+            if L["mlp"].get("shared"):
+                sf = L["mlp"]["shared"]["ff"]
+                out[p + "mlp.shared.up"], out[p + "mlp.shared.down"] = lin(sf, D), lin(D, sf)
+    return {k: v.to(torch.bfloat16).to(device) for k, v in out.items()}

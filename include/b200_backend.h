@@ -651,7 +651,8 @@ void moe_gate_up_ex(const void* h, int64_t ldh, const void* w_gate_up, const int
  * pooled_cache_update: rows whose position closes a block of `pool` positions write the mean of the block's cached keys / values into the f32 pooled
  *   caches [nb, per_block, G, dk | dv] (per_block >= ceil(block_size / pool)); entry of block b: page of its last position, index b - floor(page bs / pool).
  * paged_attention_sigmoid_pooled: out[t, h] = sum_j sigmoid(q . k_j scale + head_bias[h]) v_j over the window's tokens (window 0 = all) and the pooled
- *   entries of the blocks that end at or before position - window (pool 0 = none); q F32, caches F32 / BF16, out F32 / BF16.
+ *   entries of the blocks that end at or before position - window (pool 0 = none); q F32, caches F32 / BF16, out F32 / BF16; with BF16 q / cache / out,
+ *   dk == dv == 128, 64-token blocks and cu_seqlens_q / cu_seqlens_k (as for paged_attention_varlen) the tensor-core kernel runs.
  * latent_out_gate_ex: latent_out_gate with gate_per_element = 1 for a gate f32 [T, H dv] (one per output entry).
  * moe_route_bias: moe_route_ex with logit_bias f32 [N] (or null) added to the logits first.
  * moe_gate_up_ex act_fn 3 / glu_packed act 3: ungated experts, act = relu(W_up h)^2 with w [E, ff, D] / rows of ff entries.
@@ -670,9 +671,10 @@ void pooled_cache_update(const void* key_cache, const void* value_cache, float* 
                          int32_t table_width, const int32_t* token_seq, const int32_t* positions, const int64_t* slot_mapping, int32_t num_tokens,
                          int32_t num_kv_heads, int32_t dk, int32_t dv, int32_t block_size, int32_t pool, int32_t per_block, int32_t cache_dtype, int64_t stream);
 void paged_attention_sigmoid_pooled(void* out, const void* q, const void* key_cache, const void* value_cache, const float* pooled_keys, const float* pooled_values,
-                                    const int32_t* block_tables, int32_t table_width, const int32_t* token_seq, const int32_t* positions, const float* head_bias,
-                                    int32_t num_tokens, int32_t num_heads, int32_t num_kv_heads, int32_t dk, int32_t dv, int32_t block_size, float scale,
-                                    int32_t window, int32_t pool, int32_t per_block, int32_t q_dtype, int32_t cache_dtype, int32_t out_dtype, int64_t stream);
+                                    const int32_t* block_tables, int32_t table_width, const int32_t* token_seq, const int32_t* positions, const int32_t* cu_seqlens_q,
+                                    const int32_t* cu_seqlens_k, int32_t num_seqs, const float* head_bias, int32_t num_tokens, int32_t num_heads, int32_t num_kv_heads,
+                                    int32_t dk, int32_t dv, int32_t block_size, float scale, int32_t window, int32_t pool, int32_t per_block, int32_t q_dtype,
+                                    int32_t cache_dtype, int32_t out_dtype, int64_t stream);
 void latent_out_gate_ex(const float* src, int64_t src_stride_token, int64_t src_stride_head, const void* w_uv, const float* gate, int64_t ld_gate,
                         int32_t gate_per_element, void* out, int32_t num_tokens, int32_t num_heads, int32_t dv, int32_t rank, int32_t w_dtype, int32_t out_dtype,
                         int64_t stream);
@@ -680,6 +682,11 @@ void moe_route_bias(const float* logits, int64_t ld, const float* logit_bias, co
                     int32_t num_outputs, int32_t top, int32_t groups, int32_t keep, float scale, int32_t score_fn, int32_t normalise, int64_t stream);
 void add_rms_norm(float* x, const float* y1, int64_t ld1, const float* y2, int64_t ld2, const float* weight, void* out, const int32_t* row_index, int32_t rows,
                   int32_t n, float eps, int32_t out_dtype, int64_t stream);
+/* mla_paged_attention_window: mla_paged_attention_sink with window > 0: a row sees only the last `window` keys of its context (split-KV decode kernel only). */
+void mla_paged_attention_window(void* out, const void* q_absorbed, const void* q_pe, const void* ckv_cache, const void* kpe_cache, const uint32_t* block_tables,
+                                const uint32_t* context_lens, const uint32_t* cu_seqlens_q, const float* sink, int32_t window, int32_t num_seqs, int32_t num_rows,
+                                int32_t num_heads, int32_t kv_lora_rank, int32_t qk_rope_head_dim, int32_t block_size, int32_t max_blocks_per_seq, int64_t num_blocks,
+                                float sm_scale, int32_t dtype, void* workspace, size_t workspace_bytes, int64_t stream);
 
 #ifdef __cplusplus
 }

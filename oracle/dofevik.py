@@ -202,3 +202,13 @@ def forward(tokens: List[int], cfg: dict, w: Dict[str, torch.Tensor], hidden: Op
         if hidden is not None:
             hidden.append(x.clone())
     return scalar_norm(x, w["final.norm"], eps) @ w["head"].to(F).T
+
+
+def greedy(cfg: dict, w: Dict[str, torch.Tensor], prompt: List[int], n: int) -> List[int]:
+    """the n tokens that follow `prompt` when the largest logit is taken every time (the whole sequence is run again for every token)"""
+    toks, out = list(prompt), []
+    for _ in range(n):
+        t = int(torch.argmax(forward(toks, cfg, w)[-1]))
+        out.append(t)
+        toks.append(t)
+    return out
