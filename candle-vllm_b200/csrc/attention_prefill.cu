@@ -71,6 +71,7 @@ template <typename T> __device__ __forceinline__ uint32_t pack2(float lo, float 
 template <> __device__ __forceinline__ uint32_t pack2<__nv_bfloat16>(float lo, float hi) { __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi); return *reinterpret_cast<uint32_t*>(&v); }
 template <> __device__ __forceinline__ uint32_t pack2<__half>(float lo, float hi) { __half2 v = __floats2half2_rn(lo, hi); return *reinterpret_cast<uint32_t*>(&v); }
 __device__ __forceinline__ float fast_exp2(float x) { float y; asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x)); return y; }
+__device__ __forceinline__ float fast_tanh(float x) { float y; asm("tanh.approx.f32 %0, %1;" : "=f"(y) : "f"(x)); return y; }
 
 struct PrefillParams {
     const void* q; void* out;
@@ -88,7 +89,7 @@ struct PrefillParams {
 // With pooled caches, a row at position i also sees, like keys, the pooled entries of the blocks b with b pool + pool - 1 <= i - window; entry b lives
 // in the page of its last position at index b - floor(page 64 / pool).  Pooled tiles of 64 entries are gathered, converted to 16 bits and laid out
 // in shared memory like a page by all threads (the second stage buffer, before the page walk needs it), then take the same MMA path as a page.
-template <typename T, bool kSigmoid>
+template <typename T, bool kSigmoid, bool kPooled>
 __global__ void __launch_bounds__(kPfThreads, 2)
 paged_attn_prefill_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constant__ CUtensorMap vmap, const PrefillParams p) {
     extern __shared__ __align__(1024) uint8_t smem[];
@@ -160,17 +161,20 @@ paged_attn_prefill_kernel(const __grid_constant__ CUtensorMap kmap, const __grid
     // with a sink the running maximum starts from it and the running sum from 1 (kept by one thread of the four that share a row)
     const float sink_log2 = (!kSigmoid && p.sink) ? p.sink[head] * 1.4426950408889634f : -INFINITY;
     float m_lo = sink_log2, m_hi = sink_log2, l_lo = (sink_log2 != -INFINITY && t == 0) ? 1.f : 0.f, l_hi = l_lo;
-    const float bias_log2 = (kSigmoid && p.head_bias) ? p.head_bias[head] * 1.4426950408889634f : 0.f;
+    // sigmoid(x) = 0.5 tanh(x / 2) + 0.5: one special-function operation per weight (the weights are rounded to 16 bits for the P V product anyway)
+    const float half_bias = (kSigmoid && p.head_bias) ? 0.5f * p.head_bias[head] : 0.f;
+    const float half_scale = 0.5f * p.scale_log2 * 0.6931471805599453f;
     const int pos_lo = pos0 + r_lo, pos_hi = pos0 + r_hi;          // last visible key of each of this thread's two rows
     const int warp_min_pos = pos0 + warp * 16, warp_max_pos = pos0 + warp * 16 + 15;
     const int cs_lo = p.chunk > 0 ? (pos_lo / p.chunk) * p.chunk : 0, cs_hi = p.chunk > 0 ? (pos_hi / p.chunk) * p.chunk : 0;
     const int warp_min_cs = p.chunk > 0 ? (warp_min_pos / p.chunk) * p.chunk : 0, warp_max_cs = p.chunk > 0 ? (warp_max_pos / p.chunk) * p.chunk : 0;
     // pooled blocks a row at position x sees: those that end at or before x - window
-    auto blocks_seen = [&](int x) { return (p.kp && p.pool > 0 && p.window > 0 && x - p.window + 1 > 0) ? (x - p.window + 1) / p.pool : 0; };
+    auto blocks_seen = [&](int x) { return (kPooled && p.window > 0 && x - p.window + 1 > 0) ? (x - p.window + 1) / p.pool : 0; };
     const int seen_lo = blocks_seen(pos_lo), seen_hi = blocks_seen(pos_hi);
 
     // one 32-key half (a page's tokens, or pooled entries numbered from tok0): S = Q K^T, mask, weights, O += P V
-    auto process = [&](uint32_t kt, uint32_t vt, int tok0, bool pooled) {
+    auto process = [&](uint32_t kt, uint32_t vt, int tok0, auto pooled_tag) {
+        constexpr bool pooled = decltype(pooled_tag)::value;
         // ---- S = Q K^T : 4 n-tiles (8 tokens) x 8 k-steps -----------------------------------------------------------------
         float sacc[4][4];
 #pragma unroll
@@ -196,15 +200,15 @@ paged_attn_prefill_kernel(const __grid_constant__ CUtensorMap kmap, const __grid
             for (int e = 0; e < 2; ++e) {
                 const int tok = tok0 + nt * 8 + 2 * t + e;
                 bool ok_lo = true, ok_hi = true;
-                if (pooled) {
+                if constexpr (pooled) {
                     ok_lo = tok < seen_lo; ok_hi = tok < seen_hi;
                 } else if (need_mask) {
                     ok_lo = tok <= pos_lo && (p.window <= 0 || tok > pos_lo - p.window) && tok >= cs_lo;
                     ok_hi = tok <= pos_hi && (p.window <= 0 || tok > pos_hi - p.window) && tok >= cs_hi;
                 }
                 if constexpr (kSigmoid) {
-                    sacc[nt][e] = ok_lo ? 1.0f / (1.0f + fast_exp2(-(sacc[nt][e] * p.scale_log2 + bias_log2))) : 0.f;
-                    sacc[nt][2 + e] = ok_hi ? 1.0f / (1.0f + fast_exp2(-(sacc[nt][2 + e] * p.scale_log2 + bias_log2))) : 0.f;
+                    sacc[nt][e] = ok_lo ? fmaf(0.5f, fast_tanh(fmaf(sacc[nt][e], half_scale, half_bias)), 0.5f) : 0.f;
+                    sacc[nt][2 + e] = ok_hi ? fmaf(0.5f, fast_tanh(fmaf(sacc[nt][2 + e], half_scale, half_bias)), 0.5f) : 0.f;
                 } else {
                     sacc[nt][e] = ok_lo ? sacc[nt][e] * p.scale_log2 : -INFINITY;
                     sacc[nt][2 + e] = ok_hi ? sacc[nt][2 + e] * p.scale_log2 : -INFINITY;
@@ -239,7 +243,7 @@ paged_attn_prefill_kernel(const __grid_constant__ CUtensorMap kmap, const __grid
         // ---- O += P V : 2 k-steps (16 tokens) x 16 n-tiles (8 dims).  V rows past the context hold whatever the block contains:
         // their P is exactly 0 only if V is finite, so rows beyond klen are zeroed in shared memory first (as in the decode kernel);
         // a pooled tile is built with zeros past its last entry
-        if (!pooled && tok0 + kHalf > klen) {
+        if (!pooled && tok0 + kHalf > klen) {   // (pooled is a compile-time constant here)
             __syncwarp();
             for (int r = max(klen - tok0, 0) + (lane >> 4); r < kHalf; r += 2) {
                 const int ch = lane & 15;
@@ -263,46 +267,46 @@ paged_attn_prefill_kernel(const __grid_constant__ CUtensorMap kmap, const __grid
     };
 
     // ---- pooled entries first: tiles of 64 in the second stage buffer, which the page walk does not fill before its first iteration ---------------
-    const int seen_tile = blocks_seen(last_pos);
-    if (seen_tile > 0) {
-        const int warp_seen = blocks_seen(min(warp_max_pos, last_pos));
-        for (int b0 = 0; b0 < seen_tile; b0 += 64) {
-            {
-                const int e = threadIdx.x >> 1, part = threadIdx.x & 1;          // entry of the tile, and which 64 of its 128 entries
-                const int b = b0 + e, r = e & 31;
-                uint8_t* kdst = smem + kStage + (e >> 5) * 4 * kSub + part * kSub + r * 128;
-                uint8_t* vdst = kdst + 2 * kSub;
-                const float* ks = nullptr; const float* vs = nullptr;
-                if (b < seen_tile) {
-                    const int page = (b * p.pool + p.pool - 1) / kPg;
-                    const int64_t ent = (int64_t)table[page] * p.per_block + (b - (page * kPg) / p.pool);
-                    ks = p.kp + (ent * p.num_kv_heads + kvh) * kHd + part * 64;
-                    vs = p.vp + (ent * p.num_kv_heads + kvh) * kHd + part * 64;
-                }
-#pragma unroll
-                for (int c = 0; c < 8; ++c) {
-                    int4 kw = make_int4(0, 0, 0, 0), vw = make_int4(0, 0, 0, 0);
-                    if (ks) {
-                        const float4 k0 = reinterpret_cast<const float4*>(ks)[2 * c], k1 = reinterpret_cast<const float4*>(ks)[2 * c + 1];
-                        const float4 v0 = reinterpret_cast<const float4*>(vs)[2 * c], v1 = reinterpret_cast<const float4*>(vs)[2 * c + 1];
-                        kw = make_int4((int)pack2<T>(k0.x, k0.y), (int)pack2<T>(k0.z, k0.w), (int)pack2<T>(k1.x, k1.y), (int)pack2<T>(k1.z, k1.w));
-                        vw = make_int4((int)pack2<T>(v0.x, v0.y), (int)pack2<T>(v0.z, v0.w), (int)pack2<T>(v1.x, v1.y), (int)pack2<T>(v1.z, v1.w));
+    if constexpr (kPooled) {
+        const int seen_tile = blocks_seen(last_pos);
+        if (seen_tile > 0) {
+            const int warp_seen = blocks_seen(min(warp_max_pos, last_pos));
+            for (int b0 = 0; b0 < seen_tile; b0 += 64) {
+                {
+                    const int e = threadIdx.x >> 1, part = threadIdx.x & 1;          // entry of the tile, and which 64 of its 128 entries
+                    const int b = b0 + e, r = e & 31;
+                    uint8_t* kdst = smem + kStage + (e >> 5) * 4 * kSub + part * kSub + r * 128;
+                    const float* src[2] = {nullptr, nullptr};
+                    if (b < seen_tile) {
+                        const int page = (b * p.pool + p.pool - 1) / kPg;
+                        const int64_t ent = (int64_t)table[page] * p.per_block + (b - (page * kPg) / p.pool);
+                        src[0] = p.kp + (ent * p.num_kv_heads + kvh) * kHd + part * 64;
+                        src[1] = p.vp + (ent * p.num_kv_heads + kvh) * kHd + part * 64;
                     }
-                    *reinterpret_cast<int4*>(kdst + ((c ^ (r & 7)) << 4)) = kw;
-                    *reinterpret_cast<int4*>(vdst + ((c ^ (r & 7)) << 4)) = vw;
+#pragma unroll
+                    for (int kv = 0; kv < 2; ++kv) {                                  // keys, then values: 16 loads in flight, then convert and store
+                        float4 f[16];
+#pragma unroll
+                        for (int c = 0; c < 16; ++c) f[c] = src[kv] ? reinterpret_cast<const float4*>(src[kv])[c] : make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+                        for (int c = 0; c < 8; ++c)
+                            *reinterpret_cast<int4*>(kdst + kv * 2 * kSub + ((c ^ (r & 7)) << 4)) =
+                                make_int4((int)pack2<T>(f[2 * c].x, f[2 * c].y), (int)pack2<T>(f[2 * c].z, f[2 * c].w), (int)pack2<T>(f[2 * c + 1].x, f[2 * c + 1].y),
+                                          (int)pack2<T>(f[2 * c + 1].z, f[2 * c + 1].w));
+                    }
                 }
-            }
-            __syncthreads();
+                __syncthreads();
 #pragma unroll 1
-            for (int h = 0; h < 2; ++h) {
-                if (b0 + h * kHalf >= warp_seen) break;
-                const uint32_t kt = smem_base + kStage + h * 4 * kSub;
-                process(kt, kt + 2 * kSub, b0 + h * kHalf, true);
+                for (int h = 0; h < 2; ++h) {
+                    if (b0 + h * kHalf >= warp_seen) break;
+                    const uint32_t kt = smem_base + kStage + h * 4 * kSub;
+                    process(kt, kt + 2 * kSub, b0 + h * kHalf, std::true_type{});
+                }
+                __syncthreads();
             }
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");           // the buffer goes back to the TMA loads of the page walk
             __syncthreads();
         }
-        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");           // the buffer goes back to the TMA loads of the page walk
-        __syncthreads();
     }
 
     for (int page = page_lo, it = 0; page <= page_hi; ++page, ++it) {
@@ -316,7 +320,7 @@ paged_attn_prefill_kernel(const __grid_constant__ CUtensorMap kmap, const __grid
             if (p.window > 0 && tok0 + kHalf - 1 < warp_min_pos - p.window + 1) continue;      // entirely before every row's window
             if (tok0 + kHalf - 1 < warp_min_cs) continue;                                      // entirely before every row's chunk
             const uint32_t kt = smem_base + stage * kStage + h * 4 * kSub;
-            process(kt, kt + 2 * kSub, tok0, false);
+            process(kt, kt + 2 * kSub, tok0, std::false_type{});
         }
         __syncthreads();                                             // every warp is done with this stage before it is refilled
     }
@@ -389,10 +393,12 @@ void paged_attention_prefill_tc(void* out, const void* q, const void* kc, const 
         if (extras->pooled_keys && extras->pool > 0) { p.kp = extras->pooled_keys; p.vp = extras->pooled_values; p.pool = extras->pool; p.per_block = extras->per_block; }
     }
     const int tiles = total_q / kQTile + num_seqs;                   // >= sum of ceil(q_len / 64)
-#define PF_LAUNCH(TT, SG) do { ensure_dynamic_smem(reinterpret_cast<const void*>(paged_attn_prefill_kernel<TT, SG>), kPfSmem); \
-        paged_attn_prefill_kernel<TT, SG><<<dim3(tiles, num_heads), kPfThreads, kPfSmem, st>>>(km, vm, p); } while (0)
-    if (dtype == B200_BF16) { if (sigmoid) PF_LAUNCH(__nv_bfloat16, true); else PF_LAUNCH(__nv_bfloat16, false); }
-    else { if (sigmoid) PF_LAUNCH(__half, true); else PF_LAUNCH(__half, false); }
+#define PF_LAUNCH(TT, SG, PL) do { ensure_dynamic_smem(reinterpret_cast<const void*>(paged_attn_prefill_kernel<TT, SG, PL>), kPfSmem); \
+        paged_attn_prefill_kernel<TT, SG, PL><<<dim3(tiles, num_heads), kPfThreads, kPfSmem, st>>>(km, vm, p); } while (0)
+    const bool pooled = p.kp != nullptr && p.window > 0;                 // pooled entries come with the sigmoid form only
+    if (pooled && !sigmoid) { set_error(kErrUnsupported, "paged_attention_prefill: pooled entries need the sigmoid form"); return; }
+    if (dtype == B200_BF16) { if (pooled) PF_LAUNCH(__nv_bfloat16, true, true); else if (sigmoid) PF_LAUNCH(__nv_bfloat16, true, false); else PF_LAUNCH(__nv_bfloat16, false, false); }
+    else { if (pooled) PF_LAUNCH(__half, true, true); else if (sigmoid) PF_LAUNCH(__half, true, false); else PF_LAUNCH(__half, false, false); }
 #undef PF_LAUNCH
     count_launch();
     check_launch("paged_attention_prefill");

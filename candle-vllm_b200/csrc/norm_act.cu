@@ -360,6 +360,27 @@ add_rms_norm_kernel(float* __restrict__ x, const float* __restrict__ y1, int64_t
     }
 }
 
+
+// act 3 of glu_packed without a row factor: out = relu(x)^2 over rows of ff entries (pitch ld), four entries per thread when rows allow 16-byte loads
+template <typename TOut>
+__global__ void __launch_bounds__(256)
+relu2_rows_kernel(const float* __restrict__ x, TOut* __restrict__ out, int ff, int64_t ld, int vec) {
+    pdl_wait();
+    pdl_trigger();
+    const int64_t r = blockIdx.x;
+    const int c = (blockIdx.y * 256 + threadIdx.x) * 4;
+    if (c >= ff) return;
+    const float* src = x + r * ld + c;
+    TOut* dst = out + r * ff + c;
+    if (vec) {
+        float4 v = *reinterpret_cast<const float4*>(src);
+        v.x = fmaxf(v.x, 0.f); v.y = fmaxf(v.y, 0.f); v.z = fmaxf(v.z, 0.f); v.w = fmaxf(v.w, 0.f);
+        dst[0] = from_f32<TOut>(v.x * v.x); dst[1] = from_f32<TOut>(v.y * v.y); dst[2] = from_f32<TOut>(v.z * v.z); dst[3] = from_f32<TOut>(v.w * v.w);
+    } else {
+        for (int i = 0; i < 4 && c + i < ff; ++i) { const float v = fmaxf(src[i], 0.f); dst[i] = from_f32<TOut>(v * v); }
+    }
+}
+
 }  // namespace
 }  // namespace b200
 
@@ -498,6 +519,15 @@ void glu_packed(const float* gate_up, void* out, int64_t rows, int32_t ff, int64
                  "glu_packed: bad arguments");
     const unsigned grid = (unsigned)((rows * ff + 255) / 256);
     cudaStream_t st = as_stream(stream);
+    if (act == 3 && !row_scale && rows <= 0x7fffffff && (out_dtype == B200_F32 || out_dtype == B200_BF16)) {
+        const int vec = ff % 4 == 0 && ld % 4 == 0 && (reinterpret_cast<uintptr_t>(gate_up) & 15) == 0;
+        const dim3 g2((unsigned)rows, (unsigned)((ff + 1023) / 1024));
+        if (out_dtype == B200_F32) launch_pdl(relu2_rows_kernel<float>, g2, dim3(256), 0, st, gate_up, (float*)out, ff, ld, vec);
+        else launch_pdl(relu2_rows_kernel<__nv_bfloat16>, g2, dim3(256), 0, st, gate_up, (__nv_bfloat16*)out, ff, ld, vec);
+        count_launch();
+        check_launch("glu_packed");
+        return;
+    }
     if (out_dtype == B200_F32) launch_pdl(glu_packed_kernel<float>, dim3(grid), dim3(256), 0, st, gate_up, (float*)out, rows, ff, ld, act, limit, row_scale, scale_index);
     else if (out_dtype == B200_BF16)
         launch_pdl(glu_packed_kernel<__nv_bfloat16>, dim3(grid), dim3(256), 0, st, gate_up, (__nv_bfloat16*)out, rows, ff, ld, act, limit, row_scale, scale_index);
