@@ -1411,7 +1411,7 @@ def run_dofevik(args):
         like[("decode", "paged_attention_varlen")] = [timed(lambda: ops.paged_attention_varlen(qq[:B], kc, vc, bd, H, G, hd, hd, 64, hd ** -0.5, 0, Wn, bf), 20, 3)]
         del kc, vc, qq
         torch.cuda.empty_cache()
-        med = lambda v: sorted(v)[len(v) // 2]
+        med = lambda v: (sorted(v)[(len(v) - 1) // 2] + sorted(v)[len(v) // 2]) / 2
         esz, Wd = 2, R + dr
 
         def work(tag, key, T):

@@ -95,7 +95,7 @@ qk_head_norm_rope_cache_kernel(const float* __restrict__ proj, int64_t ld, const
 }
 
 template <typename TC>
-__global__ void __launch_bounds__(128)
+__global__ void __launch_bounds__(256)
 pooled_cache_update_kernel(const TC* __restrict__ k_cache, const TC* __restrict__ v_cache, float* __restrict__ kp, float* __restrict__ vp,
                            const int32_t* __restrict__ block_tables, int table_width, const int32_t* __restrict__ token_seq,
                            const int32_t* __restrict__ positions, const int64_t* __restrict__ slot_mapping, int nk, int nv, int block_size, int pool,
@@ -107,21 +107,24 @@ pooled_cache_update_kernel(const TC* __restrict__ k_cache, const TC* __restrict_
     if ((pos + 1) % pool) return;                          // this row closes no block
     const int64_t slot = slot_mapping[t];
     if (slot < 0) return;
+    const int i = blockIdx.y * 256 + threadIdx.x;          // one entry of the key row, then of the value row, per thread
+    if (i >= nk + nv) return;
     const int b = (pos + 1) / pool - 1;
     const int page = pos / block_size;
     const int64_t dst = (slot / block_size) * per_block + (b - (int)(((int64_t)page * block_size) / pool));
     const int32_t* table = block_tables + (int64_t)token_seq[t] * table_width;
-    const float inv = 1.0f / (float)pool;
-    for (int i = threadIdx.x; i < nk + nv; i += 128) {
-        const bool is_k = i < nk;
-        float a = 0.f;
-        for (int j = pos - pool + 1; j <= pos; ++j) {
-            const int64_t phys = (int64_t)table[j / block_size] * block_size + j % block_size;
-            a += is_k ? to_f32<TC>(k_cache[phys * nk + i]) : to_f32<TC>(v_cache[phys * nv + (i - nk)]);
-        }
-        if (is_k) kp[dst * nk + i] = a * inv;
-        else vp[dst * nv + (i - nk)] = a * inv;
+    const bool is_k = i < nk;
+    const TC* src = is_k ? k_cache + i : v_cache + (i - nk);
+    const int n = is_k ? nk : nv;
+    float a = 0.f;
+#pragma unroll 8
+    for (int j = pos - pool + 1; j <= pos; ++j) {          // a fixed order: the mean does not depend on how the prompt was cut
+        const int64_t phys = (int64_t)table[j / block_size] * block_size + j % block_size;
+        a += to_f32<TC>(src[phys * n]);
     }
+    a *= 1.0f / (float)pool;
+    if (is_k) kp[dst * nk + i] = a;
+    else vp[dst * nv + (i - nk)] = a;
 }
 
 constexpr int kMaxVPerLane = 8;      // value size <= 256
@@ -243,11 +246,13 @@ void pooled_cache_update(const void* key_cache, const void* value_cache, float* 
                  "pooled_cache_update: bad sizes (a page needs ceil(block_size / pool) pooled entries)");
     cudaStream_t st = as_stream(stream);
     const int nk = num_kv_heads * dk, nv = num_kv_heads * dv;
+    B200_REQUIRE((nk + nv + 255) / 256 <= 65535, kErrUnsupported, "pooled_cache_update: rows of %d entries", nk + nv);
+    const dim3 grid((unsigned)num_tokens, (unsigned)((nk + nv + 255) / 256));
     if (cache_dtype == B200_F32)
-        launch_pdl(pooled_cache_update_kernel<float>, dim3(num_tokens), dim3(128), 0, st, (const float*)key_cache, (const float*)value_cache, pooled_keys, pooled_values,
+        launch_pdl(pooled_cache_update_kernel<float>, grid, dim3(256), 0, st, (const float*)key_cache, (const float*)value_cache, pooled_keys, pooled_values,
                    block_tables, table_width, token_seq, positions, slot_mapping, nk, nv, block_size, pool, per_block);
     else if (cache_dtype == B200_BF16)
-        launch_pdl(pooled_cache_update_kernel<__nv_bfloat16>, dim3(num_tokens), dim3(128), 0, st, (const __nv_bfloat16*)key_cache, (const __nv_bfloat16*)value_cache,
+        launch_pdl(pooled_cache_update_kernel<__nv_bfloat16>, grid, dim3(256), 0, st, (const __nv_bfloat16*)key_cache, (const __nv_bfloat16*)value_cache,
                    pooled_keys, pooled_values, block_tables, table_width, token_seq, positions, slot_mapping, nk, nv, block_size, pool, per_block);
     else { set_error(kErrUnsupported, "pooled_cache_update: cache dtype %d", cache_dtype); return; }
     count_launch();
