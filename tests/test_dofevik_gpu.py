@@ -432,6 +432,8 @@ def test_wide_heads_on_the_tensor_core_kernel_match_the_oracle_and_the_plain_ker
     w = {k[7:]: v for k, v in S.dofevik_weights(S.dofevik_config(D, 10, [L]), 13).items() if k.startswith("l0.mix.")}
     if kind == "attention":
         w["sink"] = torch.tensor([3.0, -1.0, 5.0, 0.5][:H]).to(torch.bfloat16)
+    elif pool == 16:
+        w["pb"] = torch.tensor([-6.0, -5.5]).to(torch.bfloat16)            # weights of a few thousandths: their relative accuracy must hold
     h = torch.randn(T, D, generator=g).to(torch.bfloat16).float()
     m = L["mixer"]
     want = (O.mixer_attention if kind == "attention" else O.mixer_attention_2)(h.to(F64), torch.arange(T), w, m, 1e-6)
