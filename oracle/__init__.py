@@ -2,7 +2,7 @@
 
 TEST INFRASTRUCTURE ONLY.  Nothing under ``oracle/`` is part of the product:
 only ``tests/``, ``__graft_entry__.smoke()`` and ``bench.py``'s ``cpu_baseline`` /
-``--impl reference`` legs may import it, and there only as the checker.  The product
+``--impl reference`` legs may import it, and there only as the comparison.  The product
 path (``candle-vllm_b200``) never imports this package and has no CPU fallback.
 
 Parity status:

@@ -1,7 +1,7 @@
 /*
  * oracle/cpu_ref.c -- C restatement of the reference's CPU (candle/GGML) arithmetic for the
  * batched-decode hot path.  TEST INFRASTRUCTURE + CPU BASELINE ONLY (see oracle/__init__.py):
- * used by tests/ as a checker, and by bench.py's cpu_baseline / --impl reference legs as the
+ * used by tests/ as the comparison, and by bench.py's cpu_baseline / --impl reference legs as the
  * timed CPU arm.  The product never links or calls this file.
  *
  * The reference's CPU path cannot be compiled here (no cargo/rustc; the arithmetic lives in
