@@ -413,6 +413,43 @@ def test_many_rows_take_the_tensor_core_routes():
     assert float(e.median()) < 0.03
 
 
+def test_wide_heads_and_wide_latent_as_a_whole_model_in_unequal_batches():
+    """128-wide heads and a 512 + 64 latent: in bf16 the paged attentions run on the tensor-core kernel and the latent rows on the split-KV kernel, in f32
+    on the plain kernels.  Every expert is chosen (top == experts), so no near-tie of a router can move a row: all rows of all requests stay within rounding
+    of the oracle, whole, in portions, and side by side with other requests over pages that change hands."""
+    cfg = S.dofevik_config(256, 333, [S.dofevik_pooled_layer(4, 2, 128, window=130, pool=9, scale=0.09, experts=3, ff=64, top=3, shared_ff=128),
+                                      S.dofevik_attention_layer(4, 1, 128, 128, window=200, rot_dims=64, base=3e5, factor=2.0, scale=0.09, experts=3, ff=64, top=3),
+                                      S.dofevik_latent_layer(2, 128, 64, 128, 512, 192, window=150, scale=0.07, experts=3, ff=64, top=3, shared_ff=64)])
+    w = S.dofevik_weights(cfg, 6)
+    g = torch.Generator().manual_seed(8)
+    lens = [470, 131, 3, 260]
+    seqs = [torch.randint(0, cfg["vocab"], (n,), generator=g).tolist() for n in lens]
+    refs = [O.forward(s, cfg, w) for s in seqs]
+    plans = [[300, 1, 1, 64, 2], [1, 1, 129], [2, 1], [130, 1, 1, 1, 70, 57]]
+    for dtype, cap in ((torch.float32, 2e-4), (torch.bfloat16, 0.05)):
+        model = DofevikModel(DofevikConfig.from_dict(cfg), w, dtype=dtype, block_size=64, max_pos=512, device=DEV)
+        runner = ModelRunner(model, 18, 4, 64)
+        whole = run_schedule(runner, 9, seqs[0], [lens[0]])
+        assert float(row_errors(whole, refs[0]).max()) < cap, (dtype, "whole", float(row_errors(whole, refs[0]).max()))
+        fed, step, got = [0] * 4, 0, [[] for _ in lens]
+        for i in range(4):
+            runner.admit(i)
+        while any(f < n for f, n in zip(fed, lens)):
+            entries = []
+            for i, n in enumerate(lens):
+                if fed[i] < n and not (i == 1 and step % 3 == 1):               # request 1 sits out every third step
+                    k = min(plans[i][step] if step < len(plans[i]) else 1, n - fed[i])
+                    entries.append(dict(seq_id=i, tokens=seqs[i][fed[i]:fed[i] + k], want=list(range(k))))
+            out, at = runner.execute(entries), 0
+            for e in entries:
+                k = len(e["tokens"])
+                got[e["seq_id"]].append(out[at:at + k]); at += k; fed[e["seq_id"]] += k
+            step += 1
+        for i in range(4):
+            e = row_errors(torch.cat(got[i]), refs[i])
+            assert float(e.max()) < cap, (dtype, i, int(e.argmax()), float(e.max()))
+
+
 WIDE = [  # kind, H, G, window, pool: 128-wide heads in bf16 take the tensor-core kernel (its sink, its sigmoid form, its pooled tiles)
     ("attention", 4, 2, 100, 0), ("attention", 2, 2, 0, 0), ("attention", 4, 1, 64, 0),
     ("pooled", 4, 2, 70, 2), ("pooled", 2, 1, 100, 16), ("pooled", 2, 2, 0, 0), ("pooled", 3, 3, 33, 0), ("pooled", 2, 2, 5, 1), ("pooled", 2, 1, 64, 64),
