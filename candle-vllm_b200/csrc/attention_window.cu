@@ -127,6 +127,56 @@ pooled_cache_update_kernel(const TC* __restrict__ k_cache, const TC* __restrict_
     else vp[dst * nv + (i - nk)] = a;
 }
 
+// The same update with 16-byte reads: a warp per row of the step, a lane per group of 16 / sizeof(TC) neighbouring entries of the key row or the value
+// row (nk and nv are multiples of the group).  Every entry is still the sum of its block's positions in ascending order, so both kernels give the same bits.
+template <typename TC>
+__global__ void __launch_bounds__(256)
+pooled_cache_update_vec_kernel(const TC* __restrict__ k_cache, const TC* __restrict__ v_cache, float* __restrict__ kp, float* __restrict__ vp,
+                               const int32_t* __restrict__ block_tables, int table_width, const int32_t* __restrict__ token_seq,
+                               const int32_t* __restrict__ positions, const int64_t* __restrict__ slot_mapping, int num_tokens, int nk, int nv,
+                               int block_size, int pool, int per_block) {
+    pdl_wait();
+    pdl_trigger();
+    constexpr int VEC = 16 / (int)sizeof(TC);
+    const int t = blockIdx.x * 8 + (threadIdx.x >> 5);
+    if (t >= num_tokens) return;
+    const int pos = positions[t];
+    if ((pos + 1) % pool) return;                          // this row closes no block
+    const int64_t slot = slot_mapping[t];
+    if (slot < 0) return;
+    const int i = (blockIdx.y * 32 + (threadIdx.x & 31)) * VEC;        // first entry of the lane's group in [key row | value row]
+    if (i >= nk + nv) return;
+    const int b = (pos + 1) / pool - 1;
+    const int page = pos / block_size;
+    const int64_t dst = (slot / block_size) * per_block + (b - (int)(((int64_t)page * block_size) / pool));
+    const int32_t* table = block_tables + (int64_t)token_seq[t] * table_width;
+    const bool is_k = i < nk;
+    const TC* src = is_k ? k_cache + i : v_cache + (i - nk);
+    const int n = is_k ? nk : nv;
+    float a[VEC];
+#pragma unroll
+    for (int c = 0; c < VEC; ++c) a[c] = 0.f;
+#pragma unroll 8
+    for (int j = pos - pool + 1; j <= pos; ++j) {
+        const int64_t phys = (int64_t)table[j / block_size] * block_size + j % block_size;
+        const uint4 raw = *reinterpret_cast<const uint4*>(src + phys * n);
+        const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+            if constexpr (sizeof(TC) == 4) {
+                a[c] += __uint_as_float(w[c]);
+            } else {                                       // two bf16 in a word: the low half is the earlier entry
+                a[2 * c] += __uint_as_float(w[c] << 16);
+                a[2 * c + 1] += __uint_as_float(w[c] & 0xffff0000u);
+            }
+        }
+    }
+    const float inv = 1.0f / (float)pool;
+    float* out = is_k ? kp + dst * nk + i : vp + dst * nv + (i - nk);
+#pragma unroll
+    for (int c = 0; c < VEC; c += 4) *reinterpret_cast<float4*>(out + c) = make_float4(a[c] * inv, a[c + 1] * inv, a[c + 2] * inv, a[c + 3] * inv);
+}
+
 constexpr int kMaxVPerLane = 8;      // value size <= 256
 
 template <typename TC, typename TOut, typename TQ>
@@ -247,8 +297,17 @@ void pooled_cache_update(const void* key_cache, const void* value_cache, float* 
     cudaStream_t st = as_stream(stream);
     const int nk = num_kv_heads * dk, nv = num_kv_heads * dv;
     B200_REQUIRE((nk + nv + 255) / 256 <= 65535, kErrUnsupported, "pooled_cache_update: rows of %d entries", nk + nv);
+    const int vec = cache_dtype == B200_F32 ? 4 : 8;      // entries in 16 bytes
+    const bool wide = nk % vec == 0 && nv % vec == 0 && ((uintptr_t)key_cache | (uintptr_t)value_cache | (uintptr_t)pooled_keys | (uintptr_t)pooled_values) % 16 == 0;
     const dim3 grid((unsigned)num_tokens, (unsigned)((nk + nv + 255) / 256));
-    if (cache_dtype == B200_F32)
+    const dim3 grid_v((unsigned)((num_tokens + 7) / 8), (unsigned)(((nk + nv) / vec + 31) / 32));
+    if (cache_dtype == B200_F32 && wide)
+        launch_pdl(pooled_cache_update_vec_kernel<float>, grid_v, dim3(256), 0, st, (const float*)key_cache, (const float*)value_cache, pooled_keys, pooled_values,
+                   block_tables, table_width, token_seq, positions, slot_mapping, num_tokens, nk, nv, block_size, pool, per_block);
+    else if (cache_dtype == B200_BF16 && wide)
+        launch_pdl(pooled_cache_update_vec_kernel<__nv_bfloat16>, grid_v, dim3(256), 0, st, (const __nv_bfloat16*)key_cache, (const __nv_bfloat16*)value_cache,
+                   pooled_keys, pooled_values, block_tables, table_width, token_seq, positions, slot_mapping, num_tokens, nk, nv, block_size, pool, per_block);
+    else if (cache_dtype == B200_F32)
         launch_pdl(pooled_cache_update_kernel<float>, grid, dim3(256), 0, st, (const float*)key_cache, (const float*)value_cache, pooled_keys, pooled_values,
                    block_tables, table_width, token_seq, positions, slot_mapping, nk, nv, block_size, pool, per_block);
     else if (cache_dtype == B200_BF16)

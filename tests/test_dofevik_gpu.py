@@ -169,6 +169,35 @@ def test_sigmoid_attention_over_window_and_pooled_blocks(H, G, dk, window, pool,
     close(got, O.mixer_attention_2(h.to(F64), torch.arange(T), w, m, 1e-6), 2e-5, f"window {window} pool {pool}, portions {sizes}")
 
 
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("G,dk,dv,pool", [(2, 16, 8, 7), (3, 5, 6, 12), (1, 128, 128, 16), (2, 24, 40, 70), (4, 8, 8, 1), (1, 4, 12, 64)])
+def test_pooled_entries_are_the_means_of_their_blocks_at_their_places(G, dk, dv, pool, dtype):
+    """the pooled cache after a prompt fed in portions: the entry of block b sits in the page of the block's last position at index b - floor(page bs / pool) and
+    equals the mean of the cached rows (rows of 16-byte groups and rows of any other length take different kernels); places no block owns keep what they held"""
+    g = torch.Generator().manual_seed(G * 1000 + dk + pool)
+    bs, T, table = 64, 200, [3, 0, 2, 1]
+    per = -(-bs // pool)
+    keys, vals = torch.randn(T, G, dk, generator=g).to(dtype), torch.randn(T, G, dv, generator=g).to(dtype)
+    kc, vc = torch.zeros(4, bs, G, dk, dtype=dtype, device=DEV), torch.zeros(4, bs, G, dv, dtype=dtype, device=DEV)
+    for p in range(T):
+        kc[table[p // bs], p % bs], vc[table[p // bs], p % bs] = keys[p].to(DEV), vals[p].to(DEV)
+    kp, vp = torch.full((4, per, G, dk), 9.0, device=DEV), torch.full((4, per, G, dv), -9.0, device=DEV)
+    for at, n in _portions(T, [61, 1, 2, 70, 3]):
+        ops.pooled_cache_update(kc, vc, kp, vp, batch_of([dict(tokens=[0] * n, start=at, block_table=table, state_slot=-1, want=[])]), pool)
+    owned = set()
+    for b in range(T // pool):
+        end = b * pool + pool - 1
+        page = end // bs
+        place = (table[page], b - (page * bs) // pool)
+        owned.add(place)
+        close(kp[place], keys[b * pool:end + 1].to(F64).mean(0), 2e-6, f"mean key of block {b}")
+        close(vp[place], vals[b * pool:end + 1].to(F64).mean(0), 2e-6, f"mean value of block {b}")
+    for blk in range(4):
+        for j in range(per):
+            if (blk, j) not in owned:
+                assert float(kp[blk, j].min()) == 9.0 and float(vp[blk, j].max()) == -9.0
+
+
 def test_a_loud_token_is_seen_through_its_window_then_not_then_through_its_block():
     """one token with a loud value: inside the window it dominates the row, after leaving the window it is invisible until its block of `pool`
     positions is wholly before the window, from then on it counts with weight 1 / pool inside the block's mean -- in a prompt and token by token"""
