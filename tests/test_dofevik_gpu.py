@@ -601,12 +601,16 @@ def test_command_line_and_trace_runner(tmp_path):
     a, b = list(range(3, 43)), [9, 8, 7]
     steps = [dict(step=0, entries=[dict(id="a", tokens=a[:30], want=[0, 29]), dict(id="b", tokens=b[:1], want=[0])], end=[]),
              dict(step=1, entries=[dict(id="a", tokens=a[30:], want=[9]), dict(id="b", tokens=b[1:2], want=[])], end=["a"]),
-             dict(step=2, entries=[dict(id="b", tokens=b[2:], want=[0]), dict(id="c", tokens=a[:2], want=[1])], end=[])]
+             dict(step=2, entries=[dict(id="b", tokens=b[2:], want=[0]), dict(id="c", tokens=a[:2], want=[1])], end=["b"]),
+             # a step in which nothing is wanted, by a new request under the name of a finished one; then its next token
+             dict(step=3, entries=[dict(id="a", tokens=b[:2], want=[]), dict(id="c", tokens=a[2:5], want=[])], end=[]),
+             dict(step=4, entries=[dict(id="a", tokens=b[2:], want=[0])], end=["a", "c"])]
     out = tmp_path / "out"
     r = subprocess.run([os.path.join(root, "bin", "trace_run"), "--model", str(tmp_path), "--dtype", "float32", "--out", str(out), "--max-tokens", "128"],
                        input="\n".join(json.dumps(s) for s in steps) + "\n", capture_output=True, text=True, env=env, timeout=600)
     assert r.returncode == 0, r.stderr
-    assert [l for l in r.stdout.splitlines() if l.startswith("done")] == ["done 0", "done 1", "done 2"]
+    assert [l for l in r.stdout.splitlines() if l.startswith("done")] == [f"done {i}" for i in range(5)]
+    assert not (out / "3.f32").exists()
     ra, rb = O.forward(a, cfg, w), O.forward(b, cfg, w)
     V = cfg["vocab"]
     s0 = torch.from_numpy(np.fromfile(out / "0.f32", dtype="<f4").reshape(-1, V))
@@ -615,3 +619,5 @@ def test_command_line_and_trace_runner(tmp_path):
     close(s1, ra[39:40], TOL[torch.float32], "step 1")
     s2 = torch.from_numpy(np.fromfile(out / "2.f32", dtype="<f4").reshape(-1, V))
     close(s2, torch.stack([rb[2], ra[1]]), TOL[torch.float32], "step 2")
+    s4 = torch.from_numpy(np.fromfile(out / "4.f32", dtype="<f4").reshape(-1, V))
+    close(s4, rb[2:3], TOL[torch.float32], "step 4")
