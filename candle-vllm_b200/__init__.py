@@ -1,6 +1,6 @@
 """candle-vllm_b200 -- B200-native (sm_100a) batched-decode backend for candle-vllm.
 
-Host-side mirror of the reference's operator interface for the hot path (SURVEY.md §8b):
+Host-side mirror of the reference's operator interface for the hot path:
 ``copy_blocks`` / ``swap_blocks`` (src/backend/cache.rs, attention_rs::cache), ``PagedAttention`` +
 ``InputMetadata`` (attention-rs API used at layers/attention.rs:566-575,707-718), ``QMatMul`` /
 ``QTensor`` (candle; models/linear.rs:765-806), ``CacheEngine`` (src/scheduler/cache_engine.rs) and

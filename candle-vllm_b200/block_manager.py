@@ -1,5 +1,5 @@
 """Host-side KV block manager: block tables, copy-on-write, CPU swap and the prefix cache -- the producer of the
-``block_tables`` / ``copy_blocks`` / ``swap_blocks`` inputs of the hot path (SURVEY.md 8 f1).
+``block_tables`` / ``copy_blocks`` / ``swap_blocks`` inputs of the hot path.
 
 Behavioural mirror of the reference's ``BlockEngine`` and ``PrefixCache``
 (src/scheduler/block_engine.rs:201-1484, src/scheduler/prefix_cache.rs:36-383), written from

@@ -6,7 +6,7 @@
   swap_in / swap_out  cache_engine.rs:345-385   -> swap_blocks (K5), K then V of every layer
   copy                cache_engine.rs:387-399   -> copy_blocks (K4)
 
-Unlike the reference (SURVEY.md §3.5) the block ops must be applied on EVERY tensor-parallel rank:
+Unlike the reference the block ops must be applied on EVERY tensor-parallel rank:
 each rank owns its kv-head shard of every block.
 """
 from __future__ import annotations
@@ -54,7 +54,7 @@ def allocate_mla_cache(num_layers: int, num_blocks: int, block_size: int, kv_lor
 def turboquant_layer_shapes(mode: str, num_blocks: int, block_size: int, num_kv_heads: int, head_dim: int, num_shards: int = 1) -> Dict[str, tuple]:
     """STORAGE shapes of the TurboQuant KV cache (cache_engine.rs:401-482); ``mode`` in {"turbo8", "turbo4", "turbo3"}.  Only the
     allocation is visible in the reference -- the transform (WHT + absmax quantisation) lives in attention-rs -- so this backend
-    offers the shapes for sizing and block bookkeeping, and no kernels (DESIGN.md section 6)."""
+    offers the shapes for sizing and block bookkeeping, and no kernels."""
     if mode not in ("turbo8", "turbo4", "turbo3"):
         raise BackendError(f"unknown TurboQuant mode {mode!r}")
     kvh = max(num_kv_heads // max(num_shards, 1), 1)

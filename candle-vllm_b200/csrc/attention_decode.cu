@@ -1,7 +1,7 @@
 // attention_decode.cu -- paged-attention decode for B200: TMA-staged KV pages, split-KV persistent
 // CTAs, tensor-core QK^T / PV with warp-level online softmax, plus the split merge.
 //
-// Why this shape (DESIGN.md "paged attention decode"): the op is HBM-bound -- per layer it streams
+// Why this shape: the op is HBM-bound -- per layer it streams
 // B * ctx * 2 * kvh * 128 * 2 B of KV (537-671 MB at B=32, ctx 4-5k) against ~4 flop/B of math.
 // So the kernel is organised around keeping >= 190 KB of KV reads in flight per SM:
 //   * KV cache = 4-D tensor [num_blocks, 64, kvh, 128] (flash layout,

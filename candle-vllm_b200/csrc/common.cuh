@@ -91,7 +91,7 @@ __host__ __device__ __forceinline__ int64_t k4_index(int64_t k) { return (k & ~3
 
 static inline int ceil_div(int64_t a, int64_t b) { return (int)((a + b - 1) / b); }
 
-// ---- GGML block formats (GGUF spec) -----------------------------------
+// ---- GGML block formats -----------------------------------
 struct __align__(2) block_q4_K { __half d, dmin; uint8_t scales[12]; uint8_t qs[128]; };      // 144 B
 struct __align__(2) block_q6_K { uint8_t ql[128]; uint8_t qh[64]; int8_t scales[16]; __half d; }; // 210 B
 struct __align__(2) block_q8_0 { __half d; int8_t qs[32]; };                                   // 34 B

@@ -1,6 +1,6 @@
 // dense_gemm.cu -- dense 16-bit GEMM on tcgen05:  y[m, n] = sum_k x[m, k] * w[n, k]  (+ bias[n])      x, w f16 or bf16, fp32 accumulate
 //
-// Two users (SURVEY.md section 8, rows a13 and x1):
+// Two users:
 //   * `Linear::forward` on unquantised weights (src/openai/models/linear.rs:124-172; the reference calls cuBLAS through
 //     candle's matmul) -- BASELINE config 2 (Llama-3-8B BF16);
 //   * prefill chunks of the weight-only quantised linears (m > 64): the weights are dequantised ONCE into a 16-bit scratch

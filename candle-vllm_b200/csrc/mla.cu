@@ -1,4 +1,4 @@
-// mla.cu -- multi-head latent attention over the paged latent cache (DeepSeek-V2/V3, BASELINE config 5).
+// mla.cu -- multi-head latent attention over the paged latent cache.
 //
 // Replaces attention_rs::mla::{concat_and_cache_mla, mla_paged_decode, mla_paged_prefill} as called from
 // src/openai/models/layers/mla_attention.rs:479-552; cache shapes src/scheduler/cache_engine.rs:172-185:

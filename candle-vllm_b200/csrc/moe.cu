@@ -1,4 +1,4 @@
-// moe.cu -- fused mixture-of-experts path on GGUF expert tensors (SURVEY.md section 8 row f2): top-k routing, expert sort and the grouped
+// moe.cu -- fused mixture-of-experts path on GGUF expert tensors: top-k routing, expert sort and the grouped
 // dequant-GEMM.  Mirrors the reference's FusedMoe::forward over attention_rs::{topk::topk_softmax, moe::moe_gemm_gguf}
 // (src/openai/models/layers/moe.rs:35-45, :425-480, :1429-1482; quantized_qwen3_moe.rs:70-141; BASELINE config 4:
 // Qwen3-30B-A3B Q4_K, 128 experts, top-8).

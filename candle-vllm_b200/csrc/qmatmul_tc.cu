@@ -20,10 +20,10 @@
 //   * stream-K: the (tile, unit) space is cut into one contiguous range per CTA (whole tiles per CTA when there are >= 4
 //     tiles per SM); split tiles are reduced with fp32 red.global.add (the residual add of wo / w2 falls out for free) or
 //     written to per-CTA slabs (deterministic mode; the 16-bit-output GEMMs add a finishing pass).
-// Measured behaviour, fixes and dead ends: DESIGN.md 4.2, profiles/r01_qmatmul_tc_ncu.md.
+// Measured behaviour, fixes and dead ends: profiles/r01_qmatmul_tc_ncu.md.
 //
-// Reference semantics: QMatMul::forward (src/openai/models/linear.rs:765-806); block formats SURVEY.md
-// Appendix A.  The reference's CUDA path quantises activations to Q8_1 and uses dp4a; here activations are fp16 and
+// Reference semantics: QMatMul::forward (src/openai/models/linear.rs:765-806); block formats: the GGUF
+// specification.  The reference's CUDA path quantises activations to Q8_1 and uses dp4a; here activations are fp16 and
 // accumulation fp32 (strictly closer to the fp32 target).
 #include <cuda.h>
 

@@ -1,4 +1,4 @@
-"""Synthetic GGUF-LLaMA weights and KV state (SURVEY.md §8d): no model files, no network.
+"""Synthetic GGUF-LLaMA weights and KV state: no model files, no network.
 
 Weights are random but VALID GGML blocks generated on the device with a seeded torch generator:
 Q4_K: 12 scale bytes + 128 nibble bytes uniform, d ~ U(0.5,2)*2^-14, dmin ~ 7.5*U(0.5,2)*2^-14

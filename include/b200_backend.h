@@ -2,7 +2,7 @@
  * b200_backend.h -- C ABI of libb200backend.so: the B200-native (sm_100a) batched-decode backend
  * that drops in behind candle-vllm's `src/backend` / attention-rs FFI surface.
  *
- * Conventions (identical to the reference's `attention_rs::kernels::ffi`, SURVEY.md §8 b1):
+ * Conventions (identical to the reference's `attention_rs::kernels::ffi`):
  *   - extern "C", plain pointers and sizes, `int64_t stream` = the caller's CUstream
  *     (`*dev.cu_stream() as i64`, src/backend/cache.rs:135, gptq.rs:130);
  *   - every entry point is stream-ordered, allocation-free, host-sync-free and therefore

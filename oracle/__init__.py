@@ -5,7 +5,7 @@ only ``tests/``, ``__graft_entry__.smoke()`` and ``bench.py``'s ``cpu_baseline``
 ``--impl reference`` legs may import it, and there only as the comparison.  The product
 path (``candle-vllm_b200``) never imports this package and has no CPU fallback.
 
-Parity status (SURVEY.md §8c):
+Parity status:
   * GGML block codecs (Q4_K / Q6_K / Q8_0 dequantise) are PINNED against the
     independent llama.cpp-derived implementation in the ``gguf`` Python package
     (``gguf.quants.dequantize``) through committed fixtures in ``tests/golden/``.

@@ -2,7 +2,7 @@
 
 Oracle (test infrastructure) -- see ``oracle/__init__.py``.  PARITY UNPINNED: the kernels
 (paged_attention_v1/v2, flash varlen, FusedRope, rms_norm) are in attention-rs / candle-nn, not
-in /root/reference.  Semantics follow ``NaiveAttention::forward``
+in the reference tree.  Semantics follow ``NaiveAttention::forward``
 (src/openai/models/mod.rs:1268-1307): softmax(q k^T * scale [-> tanh softcap]) v with GQA
 ``repeat_kv`` (mod.rs:1240-1247) and scale = 1/sqrt(head_dim) (layers/attention.rs:569,891),
 applied to K/V gathered through the block table.
@@ -61,7 +61,7 @@ def paged_attention_decode(q, k_cache, v_cache, block_tables, context_lens, scal
     """One query token per sequence.  q [B, H, hd] -> out f32 [B, H, hd].
 
     ``context_lens`` INCLUDES the token being decoded (inputs.rs:393-397); its K/V must already
-    be in the cache (PagedAttention.forward writes the cache first, SURVEY.md §8 a4).
+    be in the cache (PagedAttention.forward writes the cache first).
     sliding_window w: only the last w tokens are visible.
     """
     gather = _gather_kv_flash if layout == "flash" else _gather_kv_paged

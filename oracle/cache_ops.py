@@ -2,7 +2,7 @@
 copy_blocks, swap_blocks, FP8(e4m3) KV cast.
 
 Oracle (test infrastructure) -- see ``oracle/__init__.py``.  PARITY UNPINNED for the
-kernels (they live in attention-rs @a97f519, not in /root/reference); the semantics
+kernels (they live in attention-rs @a97f519, not in the reference tree); the semantics
 follow the in-tree call sites cited on each function.
 """
 from __future__ import annotations
@@ -88,7 +88,7 @@ def f32_to_e4m3(x: np.ndarray) -> np.ndarray:
     """f32 -> u8 (e4m3fn bits).  Saturating (|x|>448 -> 448; NaN -> 0x7f), RNE, subnormals kept.
 
     The reference stores FP8 KV as U8 (src/main.rs:263-267) and passes NO scale tensor at any
-    call site (attention.rs:566-575,888-897), so scale 1.0 is assumed (SURVEY.md §8c).
+    call site (attention.rs:566-575,888-897), so scale 1.0 is assumed.
     """
     x = np.asarray(x, np.float32)
     sign = (np.signbit(x)).astype(np.uint8) << 7

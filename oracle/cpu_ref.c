@@ -6,12 +6,12 @@
  *
  * The reference's CPU path cannot be compiled here (no cargo/rustc; the arithmetic lives in
  * candle-core fork @cafd231 v0.8.3 and attention-rs @a97f519 v0.6.5, neither vendored under
- * /root/reference), so kind = "port".  PARITY UNPINNED except the block codecs (pinned against
+ * the reference tree), so kind = "port".  PARITY UNPINNED except the block codecs (pinned against
  * gguf-py through tests/golden).  What is restated and from where:
  *   - Q4_K / Q6_K block formats and Q8_K activation quantisation + integer dot: candle
  *     k_quants.rs [UPSTREAM], itself a transliteration of llama.cpp ggml-quants.c
- *     (quantize_row_q8_K_ref, ggml_vec_dot_q4_K_q8_K, ggml_vec_dot_q6_K_q8_K); formats in
- *     SURVEY.md Appendix A.  Call site: QMatMul::forward src/openai/models/linear.rs:765-806.
+ *     (quantize_row_q8_K_ref, ggml_vec_dot_q4_K_q8_K, ggml_vec_dot_q6_K_q8_K); formats as in
+ *     the GGUF specification.  Call site: QMatMul::forward src/openai/models/linear.rs:765-806.
  *   - op order / dtypes of one decoder layer: src/openai/models/quantized_llama.rs:424-506,
  *     src/openai/models/layers/attention.rs:910-1011, Mlp::forward quantized_llama.rs:32-44.
  *   - attention math: NaiveAttention::forward src/openai/models/mod.rs:1268-1307 over K/V

@@ -1,11 +1,11 @@
 """CPU oracle (TEST INFRASTRUCTURE ONLY) for the weight-only low-precision float linears of the reference:
 block-scaled FP8 (LnFp8), NVFP4 (LnNvfp4) and MXFP4 (LnMxfp4).
 
-The kernels themselves live in attention-rs (not in /root/reference), and the reference holds no tests or fixtures for
+The kernels themselves live in attention-rs (not in the reference tree), and the reference holds no tests or fixtures for
 them: PARITY UNPINNED.  This file follows the tensor layouts visible at the call sites
-  /root/reference/src/openai/models/linear.rs:944-973   (fp8: weight e4m3 [N,K], weight_scale f32 [ceil(N/by), ceil(K/bx)])
-  /root/reference/src/openai/models/linear.rs:1812-1853 (nvfp4: blocks u8 [N,K/2], scales e4m3 [N,K/16], global scale)
-  /root/reference/src/openai/models/linear.rs:1686-1700 (mxfp4: blocks u8 [N,K/2], scales e8m0 [N,K/32])
+  src/openai/models/linear.rs:944-973   (fp8: weight e4m3 [N,K], weight_scale f32 [ceil(N/by), ceil(K/bx)])
+  src/openai/models/linear.rs:1812-1853 (nvfp4: blocks u8 [N,K/2], scales e4m3 [N,K/16], global scale)
+  src/openai/models/linear.rs:1686-1700 (mxfp4: blocks u8 [N,K/2], scales e8m0 [N,K/32])
 and the published element formats (OCP MX v1.0: e2m1, e8m0; e4m3fn as in torch.float8_e4m3fn).  The element decoders are
 pinned against torch's dtypes in tests/test_oracle.py.
 """

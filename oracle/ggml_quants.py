@@ -7,13 +7,12 @@ The reference consumes GGUF tensor bytes verbatim
 ``QMatMul::from_arc`` ``src/openai/models/quantized_llama.rs:332-334``) and runs
 ``QMatMul::forward`` on an f32 activation (``src/openai/models/linear.rs:765-806``).
 The arithmetic itself lives in candle-core (fork @cafd231, v0.8.3, NOT in
-/root/reference): ``k_quants.rs`` = a Rust transliteration of llama.cpp's
-``ggml-quants.c``.  The block formats are the published GGUF spec (SURVEY.md
-Appendix A).  Pinned against ``gguf.quants.dequantize`` (``tests/golden``).
+the reference tree): ``k_quants.rs`` = a Rust transliteration of llama.cpp's
+``ggml-quants.c``.  The block formats are the published GGUF spec.  Pinned against ``gguf.quants.dequantize`` (``tests/golden``).
 
 Two matmul semantics are provided:
   * ``qmatmul_dequant``  -- y = x @ dequant(W)^T in fp64/fp32: the mathematical
-    target ("fp32 oracle" of SURVEY.md §8c).
+    target (the fp32 oracle).
   * ``qmatmul_q8k``      -- what the reference's CPU path does [UPSTREAM]: each
     activation row is quantised to Q8_K (256-wide, int8 + f32 scale) and the dot
     product is integer; reported as the reference's own noise floor.
@@ -239,7 +238,7 @@ def qmatmul_q8k(x: np.ndarray, wbytes: np.ndarray, ggml_type: int, n: int, k: in
 
 
 # --------------------------------------------------------------------------------------
-# synthetic weights (SURVEY.md §8d): random valid blocks
+# synthetic weights: random valid blocks
 # --------------------------------------------------------------------------------------
 def random_q4k(rng: np.random.Generator, n: int, k: int, d_scale: float = 2.0 ** -8) -> np.ndarray:
     """u8[n, k/256*144]: d,dmin ~ f16 U(0.5,2)*d_scale, 12 scale bytes + 128 nibble bytes uniform."""

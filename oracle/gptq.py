@@ -2,7 +2,7 @@
 
 Oracle (test infrastructure) -- see ``oracle/__init__.py``.  Formats and host-side transforms follow the
 reference: qweight u32 [K/8, N], 8 nibbles along K per word, LSB first
-(/root/reference/src/openai/models/linear.rs:225-242), scales [K/g, N]; symmetric 4-bit only, group
+(src/openai/models/linear.rs:225-242), scales [K/g, N]; symmetric 4-bit only, group
 size 64 / 128 / -1, no act-order (linear.rs:319-325).  ``marlin_permute_scales`` restates
 linear.rs:341-379; its permutation tables are pinned against the reference's own Python
 (examples/convert_awq_marlin.py:8-17) through tests/golden/marlin_perms.json.  The Marlin kernel itself
@@ -136,9 +136,9 @@ def dequant_gptq_alt(qweight: np.ndarray, qzeros: np.ndarray, scales: np.ndarray
     return ((q - z) * s).T
 
 
-# ---- Marlin checkpoint format (checkpoint_format == "marlin": tensors `B` u32 [K/16, 2N] and `s`, /root/reference/src/openai/models/linear.rs:219-251) ----
+# ---- Marlin checkpoint format (checkpoint_format == "marlin": tensors `B` u32 [K/16, 2N] and `s`, src/openai/models/linear.rs:219-251) ----
 # The tile order is defined by the Marlin project (IST-DASLab/marlin, marlin/__init__.py: `_get_perms` and `Layer.pack`; third-party, not in
-# /root/reference -- only its scale permutation is, linear.rs:341-352, and it is the same `_get_perms` function).  Restated from the published
+# the reference tree -- only its scale permutation is, linear.rs:341-352, and it is the same `_get_perms` function).  Restated from the published
 # algorithm: w [K, N] -> 16 x 16 tiles -> rows of N * 16 values -> a fixed permutation inside every 1024 values -> 8 nibbles per word, strided.
 def marlin_weight_perm() -> np.ndarray:
     perm = []

@@ -1,7 +1,7 @@
 """Absorbed multi-head latent attention over the paged latent cache, numpy fp64.
 
 Oracle (test infrastructure) -- see ``oracle/__init__.py``.  PARITY UNPINNED: the kernels live in attention-rs.  Semantics follow the call sites
-in /root/reference/src/openai/models/layers/mla_attention.rs:479-552: score = (q_absorbed . ckv + q_pe . kpe) * sm_scale over the keys gathered
+in src/openai/models/layers/mla_attention.rs:479-552: score = (q_absorbed . ckv + q_pe . kpe) * sm_scale over the keys gathered
 through the block table, softmax, out = P . ckv (the caller applies W_uv); prefill is causal with the query rows being the LAST positions of the
 sequence's context (same convention as inputs.rs:351-367)."""
 from __future__ import annotations

@@ -1,7 +1,7 @@
 """Fused mixture-of-experts (GGUF experts) restated in numpy.
 
 Oracle (test infrastructure) -- see ``oracle/__init__.py``.  Follows ``FusedMoe::forward`` (GGUF flavour,
-/root/reference/src/openai/models/layers/moe.rs:1429-1482): router logits -> ``topk_softmax`` (softmax over ALL experts, the k largest
+src/openai/models/layers/moe.rs:1429-1482): router logits -> ``topk_softmax`` (softmax over ALL experts, the k largest
 probabilities, not renormalised) -> optional ``norm_topk_prob`` / ``routed_scaling_factor`` -> per (token, slot) pair:
 ``down_e(silu(gate_e x) * up_e x) * weight`` -> sum over the k slots.  PARITY UNPINNED for the kernels (attention-rs); the routing
 convention is vLLM's topk_softmax, which attention-rs ports.  ``sort_expert_assignments`` (moe.rs:35-45) is a plain ascending sort of

@@ -5,7 +5,7 @@
                      implementation of the GGUF block formats, v0.19) + Q8_0 quantisation of a
                      random vector by gguf.quants.quantize.  Pins oracle/ggml_quants.py.
   slot_mapping.json: known answers for the slot / block-table arithmetic restated from
-                     /root/reference/src/openai/pipelines/inputs.rs:12-22, :410-430 (hand-computed
+                     src/openai/pipelines/inputs.rs:12-22, :410-430 (hand-computed
                      from the formulae; the reference holds no test vectors for them).
 The reference itself (Rust, kernels in un-vendored deps) cannot be executed here, so no vectors
 come from running it.
@@ -18,6 +18,8 @@ from gguf import GGMLQuantizationType as T
 from gguf import quants
 
 HERE = os.path.dirname(os.path.abspath(__file__))
+# the reference project's AWQ -> Marlin converter (a checkout of the reference beside this repository, or REFERENCE_ROOT)
+REF_CONVERTER = os.path.join(os.environ.get("REFERENCE_ROOT", os.path.join(HERE, "..", "..", "..", "reference")), "examples", "convert_awq_marlin.py")
 
 
 def main():
@@ -60,10 +62,10 @@ if __name__ == "__main__":
 
 def marlin_perms():
     """tests/golden/marlin_perms.json: the scale permutation tables produced by EXECUTING the reference's own
-    Python (`get_scale_perms`, /root/reference/examples/convert_awq_marlin.py:8-17; the function source is
+    Python (`get_scale_perms`, examples/convert_awq_marlin.py:8-17; the function source is
     extracted with `ast` because the module imports safetensors)."""
     import ast
-    src = open("/root/reference/examples/convert_awq_marlin.py").read()
+    src = open(REF_CONVERTER).read()
     fn = [n for n in ast.parse(src).body if isinstance(n, ast.FunctionDef) and n.name == "get_scale_perms"][0]
     ns = {"List": list}
     exec(compile(ast.Module(body=[fn], type_ignores=[]), "ref", "exec"), ns)
@@ -72,13 +74,13 @@ def marlin_perms():
         json.dump({"scale_perm": sp, "scale_perm_single": sps, "source": "examples/convert_awq_marlin.py:8-17 (executed)"}, f)
 
 
-if __name__ == "__main__" and os.path.exists("/root/reference/examples/convert_awq_marlin.py"):
+if __name__ == "__main__" and os.path.exists(REF_CONVERTER):
     marlin_perms()
 
 
 def awq_zero_points():
     """tests/golden/awq_zero_points.json: AWQ-packed zero points and what the reference's offline converter turns them into
-    (`awq_to_marlin_zero_points`, /root/reference/examples/convert_awq_marlin.py:99-113, EXECUTED here with safetensors
+    (`awq_to_marlin_zero_points`, examples/convert_awq_marlin.py:99-113, EXECUTED here with safetensors
     stubbed out) -- the layout `marlin_awq_4bit_*` takes as `qzeros`."""
     import importlib.util
     import sys
@@ -89,7 +91,7 @@ def awq_zero_points():
     from oracle import gptq as OG
     for m in ("safetensors", "safetensors.torch"):
         mod = types.ModuleType(m); mod.load_file = mod.save_file = None; sys.modules.setdefault(m, mod)
-    spec = importlib.util.spec_from_file_location("conv", "/root/reference/examples/convert_awq_marlin.py")
+    spec = importlib.util.spec_from_file_location("conv", REF_CONVERTER)
     conv = importlib.util.module_from_spec(spec); spec.loader.exec_module(conv)
     zp = np.random.default_rng(0).integers(0, 16, (3, 128), dtype=np.uint8)
     packed = OG.pack_awq(zp)
@@ -98,5 +100,5 @@ def awq_zero_points():
         json.dump({"zp": zp.tolist(), "awq_packed": packed.tolist(), "marlin_zp": ref.tolist()}, f)
 
 
-if __name__ == "__main__" and os.path.exists("/root/reference/examples/convert_awq_marlin.py"):
+if __name__ == "__main__" and os.path.exists(REF_CONVERTER):
     awq_zero_points()

@@ -1,5 +1,5 @@
 """GPU parity: paged attention decode (K1) and chunked prefill (K2) through the C ABI vs the fp64
-oracle.  Tolerance (SURVEY.md §8c): <= 2e-3 abs on bf16 I/O for O(1) values = half a bf16 ulp at 1.0
+oracle.  Tolerance: <= 2e-3 abs on bf16 I/O for O(1) values = half a bf16 ulp at 1.0
 plus fp32-accumulation noise; we assert max-abs <= 2e-2 * max|out| elementwise and a tight
 rel-Frobenius bound (the output itself is rounded to bf16: rel step 2^-8 = 3.9e-3)."""
 import numpy as np

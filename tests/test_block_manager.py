@@ -1,6 +1,6 @@
 """Host-side block manager / prefix cache: the reference's own known-answer tests restated
 (src/scheduler/block_engine.rs:1537-1751, src/scheduler/prefix_cache.rs:401-599 -- the only
-golden tests the reference holds for the inputs of the hot path, SURVEY.md 8c) plus copy-on-write, swap and conservation checks."""
+golden tests the reference holds for the inputs of the hot path) plus copy-on-write, swap and conservation checks."""
 import numpy as np
 import pytest
 

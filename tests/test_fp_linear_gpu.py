@@ -2,7 +2,7 @@
 oracle (oracle/fp_formats.py; parity unpinned upstream, element formats pinned to torch / OCP tables in test_oracle.py).
 Tolerances: the SIMT kernels decode weights exactly and accumulate in fp32 -> the result differs from the fp64 target only
 by fp32 summation noise and ONE final rounding to the activation dtype (rel-Frobenius <= 2.5e-3 bf16, 4e-4 f16).  The tcgen05
-block-FP8 path (any m, 64 rows per pass) rounds scaled weights and activations to fp16 first: rel-Frobenius <= 1e-3 on f16 I/O (SURVEY.md 8c)."""
+block-FP8 path (any m, 64 rows per pass) rounds scaled weights and activations to fp16 first: rel-Frobenius <= 1e-3 on f16 I/O."""
 import os
 
 import numpy as np

@@ -1,4 +1,4 @@
-"""GPU parity of multi-head latent attention (SURVEY.md 8 f3): concat_and_cache_mla (bit-exact), absorbed MLA decode on the tensor-core split-KV
+"""GPU parity of multi-head latent attention: concat_and_cache_mla (bit-exact), absorbed MLA decode on the tensor-core split-KV
 kernel and causal prefill on the generic kernel, against oracle/mla.py.  Tolerance as for paged attention (16-bit P and output)."""
 import numpy as np
 import pytest

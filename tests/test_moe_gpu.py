@@ -1,4 +1,4 @@
-"""GPU parity of the fused MoE path on GGUF experts (SURVEY.md 8 f2): topk_softmax, sort_expert_assignments, the grouped dequant-GEMM
+"""GPU parity of the fused MoE path on GGUF experts: topk_softmax, sort_expert_assignments, the grouped dequant-GEMM
 (tcgen05, device-side item list) and the whole FusedMoe block against oracle/moe.py.  Tolerance: the QMatMul contract (fp16 operands,
 fp32 accumulate) -> rel-Frobenius 1e-3 per GEMM, 2e-3 for the block (three chained GEMMs)."""
 import numpy as np

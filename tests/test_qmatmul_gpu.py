@@ -1,5 +1,5 @@
 """GPU parity: QMatMul::forward (K6) for GGML Q4_K / Q6_K / Q8_0 through the C ABI vs the fp64
-dequant-matmul oracle.  Tolerance (SURVEY.md §8c): rel-Frobenius <= 1e-3; the reference's own
+dequant-matmul oracle.  Tolerance: rel-Frobenius <= 1e-3; the reference's own
 8-bit-activation path (Q8_K oracle) is reported alongside as its noise floor (~4e-3..7e-3)."""
 import numpy as np
 import pytest

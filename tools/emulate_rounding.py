@@ -5,7 +5,7 @@ Runs the numpy oracle (oracle/llama.py) on a 2-layer model with Llama-3-8B layer
 Q6_K lm_head with 16 384 rows, ctx ~ 4 k) three ways and reports max|err| / max|logit| and rel-Frobenius against the exact (fp64
 dequant-matmul) result:
   * fp16 operands: activations AND dequantised weights rounded once to fp16, exact accumulation -- the numerical contract of this
-    repo's QMatMul (DESIGN.md section 2) with every other source of error removed: the floor of the design;
+    repo's QMatMul with every other source of error removed: the floor of the design;
   * q8k: the reference's own CPU/GGML semantics (activations quantised to Q8_K, integer dot) -- the reference's noise floor.
 Used to justify the tolerance of tests/test_llama_gpu.py::test_decode_at_metric_shapes_matches_oracle.  ~3 minutes on 8 cores.
 """
